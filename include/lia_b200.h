@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define LIA_ABI_VERSION 7
+#define LIA_ABI_VERSION 8
 
 typedef void* lia_stream_t; /* cudaStream_t */
 
@@ -322,6 +322,10 @@ int lia_gated_act(const void* in, int ld, int up_off, void* out, int act_f32, in
 
 /* softmax over E fp32 logits per row, the `top` largest (lowest index first on ties), divided by their sum + 1e-20 */
 int lia_router_topk(const float* logits, int* idx, float* wt, int M, int E, int top, lia_stream_t stream);
+/* the same with a per-expert correction (may be NULL) added to the scores for the CHOICE only, and the weights = the chosen
+ * experts' plain scores, divided by their sum + 1e-20 only if renorm != 0 */
+int lia_router_topk_ext(const float* logits, const float* correction, int renorm, int* idx, float* wt, int M, int E, int top,
+                        lia_stream_t stream);
 /* (token, choice) pairs grouped by expert into tiles of lia_moe_tile_rows() rows: perm[n_tiles * rows] (pair or -1),
  * tile_expert[n_tiles] (expert or -1), pos_of[pairs] (place of a pair in perm).
  * n_tiles >= (pairs + min(E, pairs) * (rows - 1)) / rows. */
@@ -334,6 +338,11 @@ int lia_moe_plan(const int* idx, int pairs, int E, int n_tiles, int* perm, int* 
 int lia_moe_gemm(const void* A, int a_f32, int lda, const void* W, int w_f32, long long w_expert_stride, void* C, int c_f32, int ldc,
                  const int* perm, const int* tile_expert, int n_tiles, const int* idx, const float* wt, int pairs, int top, int N, int K,
                  int up, int act, lia_stream_t stream);
+/* the same; gated != 0 (up only): W is [E][2N][K], N gate rows then N up rows, and C = act(gate sum) * (up sum); pairs and
+ * tiles of experts >= n_real (experts without weights: lia_moe_combine_ext serves them) are skipped */
+int lia_moe_gemm_ext(const void* A, int a_f32, int lda, const void* W, int w_f32, long long w_expert_stride, void* C, int c_f32, int ldc,
+                     const int* perm, const int* tile_expert, int n_tiles, const int* idx, const float* wt, int pairs, int top, int N, int K,
+                     int up, int act, int gated, int n_real, lia_stream_t stream);
 /* dst[place] = src[perm[place] / top] (zeros where perm is -1): the experts' inputs in the plan's order */
 int lia_moe_gather(const void* src, int act_f32, const int* perm, void* dst, int places, int W, int top, lia_stream_t stream);
 /* C[rows of expert e] = A[rows of expert e] @ W[e].T (bf16, lia_gemm_bf16 per expert): expert e owns the next
@@ -344,16 +353,21 @@ int lia_moe_expert_gemms(const void* A, const void* W, long long w_expert_stride
  * wt[pair] * ypair[pos_of[pair]] */
 int lia_moe_combine(const void* ypair, int ypair_f32, const int* pos_of, const float* wt, const void* shared, int shared_f32, float* y, int M,
                     int W, int top, lia_stream_t stream);
+/* the same with identity experts: a pair whose idx[pair] >= n_real contributes wt[pair] * h[m] (h: the experts' input, of the
+ * activations' type like `shared`), and ypair is not read for it */
+int lia_moe_combine_ext(const void* ypair, int ypair_f32, const int* pos_of, const float* wt, const void* shared, int act_f32, const int* idx,
+                        int n_real, const void* h, float* y, int M, int W, int top, lia_stream_t stream);
 
 /* Short causal convolution (taps <= 8, weights [channels][taps], last column = current token) + SiLU over the q | k | v
  * channels of a projection's output y (row stride ld, column offsets given; q and k have G heads of dim, v has H of vdim);
  * q and k divided by sqrt(sum of squares + unit_eps) per head, q times q_scale; gates [M][2H] hold W_b h | W_a h on entry and
  * beta = sigmoid(.) | g = exp(-exp(a_log) * softplus(. + dt_bias)) on return.  conv_state [slot][taps-1][channels] fp32 holds
- * the inputs before each portion; lia_conv_state_update (after lia_conv_prep) moves it past the step's portions. */
+ * the inputs before each portion; lia_conv_state_update (after lia_conv_prep or lia_qkv_prep) moves it past the step's portions
+ * (nq, nk, nv channels of q, k, v at the given column offsets). */
 int lia_conv_prep(const void* y, int y_f32, int ld, int q_off, int k_off, int v_off, const float* wconv, const float* conv_state,
                   const int* meta, float* gates, const float* a_log, const float* dt_bias, float* qk, float* v, int M, int G, int H,
                   int dim, int vdim, int taps, float q_scale, float unit_eps, lia_stream_t stream);
-int lia_conv_state_update(const void* y, int y_f32, int ld, int q_off, int k_off, int v_off, int nqk, int nv, float* conv_state,
+int lia_conv_state_update(const void* y, int y_f32, int ld, int q_off, int k_off, int v_off, int nq, int nk, int nv, float* conv_state,
                           const int* segs, int nseg, int taps, lia_stream_t stream);
 /* Matrix-state recurrence over every portion; state_S [slot][H][vdim][dim] fp32, o [rows][H * vdim] fp32.
  * gates == NULL:  S = decay[h] S + k v^T, o = S^T q.   gates [rows][2H] = beta | g:  the gated delta rule
@@ -380,6 +394,42 @@ int lia_window_attn(const void* q, int ldq, int act_f32, const void* kcache, lon
                     long long v_slot_stride, const int* meta, const float* temp, void* out, float* workspace, int M, int H, int G, int dim,
                     int vdim, int window, float scale, float softcap, int heads_per_block, int rows_per_block, int nsplit,
                     lia_stream_t stream);
+/* lia_window_attn with more in the score and on the way out (each pointer may be NULL): slopes[h] * (pos - j) is taken off the
+ * (capped) score; exp(sink[h]) joins the softmax's denominator as a term without key or value; the output is multiplied by a
+ * gate -- gate_mode 1: fp32 gate[row][h]; 2: sigmoid(gate[row][h * vdim + c]) of the activations' type with row stride ldg.
+ * window <= 0: every row sees its whole history.  q_f32 != 0: the queries are fp32 whatever the caches' type. */
+int lia_window_attn_ext(const void* q, int ldq, int q_f32, int act_f32, const void* kcache, long long k_slot_stride, const void* vcache,
+                        long long v_slot_stride, const int* meta, const float* temp, const float* slopes, const float* sink, const void* gate,
+                        int gate_mode, int ldg, void* out, float* workspace, int M, int H, int G, int dim, int vdim, int window, float scale,
+                        float softcap, int heads_per_block, int rows_per_block, int nsplit, lia_stream_t stream);
+/* What turns the q | k | v columns of a projection's output y (row stride ld) into attention inputs, per token row with
+ * meta[row] = {slot, position}; each step is optional and they come in this order:
+ *   bias [H*dim + G*dim + G*vdim] added;
+ *   a short causal convolution over time per channel (taps <= 8, wconv [channels][taps], last column = current token; the
+ *   taps - 1 outputs of the projection before a portion come from conv_state [slot][taps-1][channels] fp32, kept current by
+ *   lia_conv_state_update; what lies before the sequence's start is zero);
+ *   RMS norm of q and of k -- norm_mode 1: over the whole projection, weights [H*dim] and [G*dim]; 2: per head, weights [dim];
+ *   q times 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1) (temp_every > 0);
+ *   rotation of the first rot_dims channels of every q and k head by pos * freq[i] (freq: rot_dims/2 doubles), pairs
+ *   (2i, 2i+1), or (i, i + rot_dims/2) if rot_halves != 0; cos and sin times rot_mag;
+ *   values -- vmix_mode 1: copied to v_first [M][G*vdim] fp32; 2: v = (1 - lambda) v + lambda v_first.
+ * q goes to q_out [M][H*dim] fp32, k and v to the caches [slot][capacity][G*dim | G*vdim] of the activations' type. */
+int lia_qkv_prep(const void* y, int act_f32, int ld, int q_off, int k_off, int v_off, const float* bias, const float* wconv,
+                 const float* conv_state, int taps, int norm_mode, const float* qnorm_w, const float* knorm_w, float eps, float temp_coef,
+                 int temp_every, const double* freq, int rot_dims, int rot_halves, float rot_mag, int vmix_mode, float lambda, float* v_first,
+                 const int* meta, float* q_out, void* kcache, long long k_slot_stride, void* vcache, long long v_slot_stride, int M, int H,
+                 int G, int dim, int vdim, lia_stream_t stream);
+
+/* x_new = x + w * g / sqrt(mean(g^2) + eps) with g = y * sigmoid(r + rb) (r, rb may be NULL: no gate; y NULL: nothing added;
+ * r has row stride ldr and the activations' type).  stack == NULL: x = x_new.  Else stack[n_mix - 1] = x_new and
+ * x = sum_{j < n_mix} mix[j] * stack[j] (stack: [n][rows][W] fp32 with the given stride between entries).  h (may be NULL)
+ * receives x in the activations' type. */
+int lia_gated_rms_add(float* x, const void* y, int y_f32, const void* r, int ldr, const float* rb, const float* w, float* stack,
+                      long long stack_stride, int n_mix, const float* mix, void* h, int act_f32, int rows, int W, float eps,
+                      lia_stream_t stream);
+/* out[m] = a N(z) + b N(z^2) + c N(z^3) + e over z = in[m][:F] (row stride ld), powers element by element,
+ * N(u) = u / sqrt(mean(u^2) + eps); coef = {a, b, c, e} fp32 on the device */
+int lia_poly_norm(const void* in, int ld, const float* coef, void* out, int act_f32, int M, int F, float eps, lia_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -33,8 +33,8 @@ __device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }
 constexpr int MAX_TAPS = 8;
 
 struct ConvCols {          // where the q, k, v channels sit in a row of the projection's output
-  int q_off, k_off, v_off, nqk, nv;          // nqk = G * dim channels each for q and k, nv = H * vdim
-  __device__ __forceinline__ int col(int c) const { return c < nqk ? q_off + c : (c < 2 * nqk ? k_off + (c - nqk) : v_off + (c - 2 * nqk)); }
+  int q_off, k_off, v_off, nq, nk, nv;       // channels of q, of k and of v
+  __device__ __forceinline__ int col(int c) const { return c < nq ? q_off + c : (c < nq + nk ? k_off + (c - nq) : v_off + (c - nq - nk)); }
 };
 
 // Block per token row.  meta[row] = {slot, position}; rows of one portion are consecutive and so are their positions.
@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(256) conv_prep_kernel(const T* __restrict__ y,
   extern __shared__ float ch[];                 // C channels after convolution and SiLU
   const int row = blockIdx.x;
   const int slot = meta[2 * row], pos = meta[2 * row + 1];
-  const int C = 2 * cc.nqk + cc.nv;
+  const int C = cc.nq + cc.nk + cc.nv;
   int inside = 1;                               // rows row-1 .. row-(inside-1) belong to this portion
   while (inside < taps && row - inside >= 0 && meta[2 * (row - inside)] == slot && meta[2 * (row - inside) + 1] == pos - inside) ++inside;
   const float* st = state + (size_t)slot * (taps - 1) * C;
@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(256) conv_prep_kernel(const T* __restrict__ y,
     }
     acc = silu(acc);
     ch[c] = acc;
-    if (c >= 2 * cc.nqk) v[(size_t)row * cc.nv + c - 2 * cc.nqk] = acc;
+    if (c >= cc.nq + cc.nk) v[(size_t)row * cc.nv + c - cc.nq - cc.nk] = acc;
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(256) conv_prep_kernel(const T* __restrict__ y,
     for (int i = lane; i < dim; i += 32) ss += ch[hd * dim + i] * ch[hd * dim + i];
     ss = warp_sum(ss);
     const float inv = (hd < G ? q_scale : 1.0f) / sqrtf(ss + unit_eps);
-    for (int i = lane; i < dim; i += 32) qk[(size_t)row * 2 * cc.nqk + hd * dim + i] = ch[hd * dim + i] * inv;
+    for (int i = lane; i < dim; i += 32) qk[(size_t)row * (cc.nq + cc.nk) + hd * dim + i] = ch[hd * dim + i] * inv;
   }
   for (int h = threadIdx.x; h < H; h += 256) {
     float* gr = gates + (size_t)row * 2 * H;
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(256) conv_state_update_kernel(const T* __restr
                                                                 const int* __restrict__ segs, int taps) {
   const int seg = blockIdx.y;
   const int slot = segs[4 * seg], row0 = segs[4 * seg + 2], len = segs[4 * seg + 3];
-  const int C = 2 * cc.nqk + cc.nv;
+  const int C = cc.nq + cc.nk + cc.nv;
   const int c = blockIdx.x * 256 + threadIdx.x;
   if (c >= C) return;
   float* st = state + (size_t)slot * (taps - 1) * C;
@@ -390,9 +390,9 @@ extern "C" int lia_conv_prep(const void* y, int y_f32, int ld, int q_off, int k_
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LIA_CHECK_ARG(y && wconv && conv_state && meta && gates && a_log && dt_bias && qk && v, "lia_conv_prep: null pointer");
   LIA_CHECK_ARG(M > 0 && G > 0 && H > 0 && H % G == 0 && dim > 0 && vdim > 0 && taps >= 1 && taps <= MAX_TAPS, "lia_conv_prep: bad shape G=%d H=%d dim=%d vdim=%d taps=%d", G, H, dim, vdim, taps);
-  ConvCols cc{q_off, k_off, v_off, G * dim, H * vdim};
-  const size_t smem = (size_t)(2 * cc.nqk + cc.nv) * sizeof(float);
-  LIA_CHECK_ARG(smem <= 160 * 1024, "lia_conv_prep: %d channels do not fit shared memory", 2 * cc.nqk + cc.nv);
+  ConvCols cc{q_off, k_off, v_off, G * dim, G * dim, H * vdim};
+  const size_t smem = (size_t)(cc.nq + cc.nk + cc.nv) * sizeof(float);
+  LIA_CHECK_ARG(smem <= 160 * 1024, "lia_conv_prep: %d channels do not fit shared memory", cc.nq + cc.nk + cc.nv);
   if (y_f32) {
     if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(conv_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     conv_prep_kernel<float><<<M, 256, smem, stream>>>(reinterpret_cast<const float*>(y), ld, cc, wconv, conv_state, meta, gates, a_log, dt_bias, qk, v, G, H, dim, vdim, taps, q_scale, unit_eps);
@@ -404,13 +404,13 @@ extern "C" int lia_conv_prep(const void* y, int y_f32, int ld, int q_off, int k_
   return LIA_OK;
 }
 
-extern "C" int lia_conv_state_update(const void* y, int y_f32, int ld, int q_off, int k_off, int v_off, int nqk, int nv, float* conv_state,
+extern "C" int lia_conv_state_update(const void* y, int y_f32, int ld, int q_off, int k_off, int v_off, int nq, int nk, int nv, float* conv_state,
                                      const int* segs, int nseg, int taps, lia_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  LIA_CHECK_ARG(y && conv_state && segs && nseg > 0 && nseg <= 65535 && nqk > 0 && nv > 0 && taps >= 1 && taps <= MAX_TAPS, "lia_conv_state_update: bad arguments");
+  LIA_CHECK_ARG(y && conv_state && segs && nseg > 0 && nseg <= 65535 && nq > 0 && nk > 0 && nv > 0 && taps >= 1 && taps <= MAX_TAPS, "lia_conv_state_update: bad arguments");
   if (taps == 1) return LIA_OK;
-  ConvCols cc{q_off, k_off, v_off, nqk, nv};
-  dim3 grid((2 * nqk + nv + 255) / 256, nseg);
+  ConvCols cc{q_off, k_off, v_off, nq, nk, nv};
+  dim3 grid((nq + nk + nv + 255) / 256, nseg);
   if (y_f32) conv_state_update_kernel<float><<<grid, 256, 0, stream>>>(reinterpret_cast<const float*>(y), ld, cc, conv_state, segs, taps);
   else conv_state_update_kernel<bf16><<<grid, 256, 0, stream>>>(reinterpret_cast<const bf16*>(y), ld, cc, conv_state, segs, taps);
   LIA_LAUNCH_CHECK();

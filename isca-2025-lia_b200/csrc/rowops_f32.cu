@@ -1,6 +1,7 @@
 // Row operations of models that keep their residual stream in 32-bit floats: RMS norms with a scalar or a per-channel
 // weight (fused with the residual add that follows a sublayer and with the norm that precedes the next one), the token
-// embedding with its norm, a gated feed-forward activation with clamps, a projection onto a handful of outputs with the
+// embedding with its norm, the gated, normed residual update with a weighted mix of all earlier layers' results, the
+// polynomial activation between norms, a gated feed-forward activation with clamps, a projection onto a handful of outputs with the
 // gate non-linearities in its epilogue, a plain strided-batched projection on the CUDA cores (true 32-bit products and
 // sums: the exact path, and the carrier of shapes the tensor-core GEMM does not take), and a 32-bit argmax.
 //
@@ -83,6 +84,73 @@ __global__ void __launch_bounds__(256) rms_add_norm_kernel(float* __restrict__ x
   ss = block_sum<256>(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)W + eps);
   for (int i = threadIdx.x; i < W; i += 256) stf(h + base + i, xs[i] * inv * w_pre[w_pre_n == 1 ? 0 : i]);
+}
+
+// The residual update of designs that norm a sublayer's OUTPUT and gate it first, and that hand on a weighted mix of all
+// earlier layers' results instead of the last one:
+//   g     = y * sigmoid(r + rb)                       (r null: g = y; y null: nothing is added)
+//   x_new = x + w * g / sqrt(mean(g^2) + eps)
+//   stack null:  x = x_new
+//   else:        stack[n_mix - 1][row] = x_new;  x = sum_{j < n_mix} mix[j] * stack[j][row]
+//   h null or    h = x in the activations' type
+// Block per row; `gs` (dynamic shared memory, W floats) keeps g between the two passes.
+template <typename TY, typename TH>
+__global__ void __launch_bounds__(256) gated_rms_add_kernel(float* __restrict__ x, const TY* __restrict__ y, const TH* __restrict__ r, int ldr,
+                                                            const float* __restrict__ rb, const float* __restrict__ w, float* __restrict__ stack,
+                                                            long long stack_stride, int n_mix, const float* __restrict__ mix, TH* __restrict__ h,
+                                                            int W, float eps) {
+  extern __shared__ float gs[];
+  __shared__ float red[8];
+  const size_t row = blockIdx.x, base = row * W;
+  float inv = 0.f;
+  if (y != nullptr) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < W; i += 256) {
+      float g = ldf(y + base + i);
+      if (r != nullptr) g *= 1.0f / (1.0f + expf(-(ldf(r + row * ldr + i) + (rb ? rb[i] : 0.f))));
+      gs[i] = g;
+      ss += g * g;
+    }
+    ss = block_sum<256>(ss, red);
+    inv = 1.0f / sqrtf(ss / (float)W + eps);
+  }
+  for (int i = threadIdx.x; i < W; i += 256) {
+    float v = x[base + i];
+    if (y != nullptr) v += gs[i] * inv * w[i];
+    if (stack != nullptr) {
+      stack[(size_t)(n_mix - 1) * stack_stride + base + i] = v;
+      float s = 0.f;
+      for (int j = 0; j < n_mix - 1; ++j) s = fmaf(mix[j], stack[(size_t)j * stack_stride + base + i], s);
+      v = fmaf(mix[n_mix - 1], v, s);
+    }
+    if (y != nullptr || stack != nullptr) x[base + i] = v;
+    if (h != nullptr) stf(h + base + i, v);
+  }
+}
+
+// out = a N(z) + b N(z^2) + c N(z^3) + e, powers taken element by element, N(u) = u / sqrt(mean(u^2) + eps) over the row
+// of F numbers; coef = {a, b, c, e} on the device.  Block per row: one pass for the three sums of squares, one for the output.
+template <typename T>
+__global__ void __launch_bounds__(256) poly_norm_kernel(const T* __restrict__ in, int ld, const float* __restrict__ coef, T* __restrict__ out, int F,
+                                                        float eps) {
+  __shared__ float red[8];
+  const T* z = in + (size_t)blockIdx.x * ld;
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  for (int i = threadIdx.x; i < F; i += 256) {
+    const float v = ldf(z + i), v2 = v * v;
+    s1 += v2;
+    s2 += v2 * v2;
+    s3 += v2 * v2 * v2;
+  }
+  s1 = block_sum<256>(s1, red);
+  s2 = block_sum<256>(s2, red);
+  s3 = block_sum<256>(s3, red);
+  const float a = coef[0] / sqrtf(s1 / (float)F + eps), b = coef[1] / sqrtf(s2 / (float)F + eps), c = coef[2] / sqrtf(s3 / (float)F + eps);
+  const float e = coef[3];
+  for (int i = threadIdx.x; i < F; i += 256) {
+    const float v = ldf(z + i);
+    stf(out + (size_t)blockIdx.x * F + i, fmaf(v, fmaf(v, fmaf(v, c, b), a), e));
+  }
 }
 
 // h[r] = w * x[rows[r]] / sqrt(mean^2 + eps): the norm of a few selected rows (the positions whose logits are asked for)
@@ -359,6 +427,40 @@ extern "C" int lia_rms_add_norm(float* x, const void* y, int y_f32, const float*
   else if (h_f32) LIA_RAN(bf16, float);
   else LIA_RAN(bf16, bf16);
 #undef LIA_RAN
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+extern "C" int lia_gated_rms_add(float* x, const void* y, int y_f32, const void* r, int ldr, const float* rb, const float* w, float* stack,
+                                 long long stack_stride, int n_mix, const float* mix, void* h, int act_f32, int rows, int W, float eps,
+                                 lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(x && (y || stack || h), "lia_gated_rms_add: nothing to do");
+  LIA_CHECK_ARG(!y || w, "lia_gated_rms_add: the norm after the sublayer needs its weight");
+  LIA_CHECK_ARG(!r || (y && ldr >= W), "lia_gated_rms_add: a gate needs a sublayer output and a row stride >= W");
+  LIA_CHECK_ARG(!stack || (mix && n_mix >= 1 && stack_stride >= (long long)rows * W), "lia_gated_rms_add: bad stack of earlier results");
+  LIA_CHECK_ARG(rows > 0 && W > 0 && (size_t)W * 4 <= 160 * 1024, "lia_gated_rms_add: bad shape rows=%d W=%d", rows, W);
+  const size_t smem = (size_t)W * sizeof(float);
+#define LIA_GRA(TY, TH)                                                                                                      \
+  do {                                                                                                                       \
+    if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(gated_rms_add_kernel<TY, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    gated_rms_add_kernel<TY, TH><<<rows, 256, smem, stream>>>(x, reinterpret_cast<const TY*>(y), reinterpret_cast<const TH*>(r), ldr, rb, w, stack, \
+                                                              stack_stride, n_mix, mix, reinterpret_cast<TH*>(h), W, eps);    \
+  } while (0)
+  if (y_f32 && act_f32) LIA_GRA(float, float);
+  else if (y_f32) LIA_GRA(float, bf16);
+  else if (act_f32) LIA_GRA(bf16, float);
+  else LIA_GRA(bf16, bf16);
+#undef LIA_GRA
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+extern "C" int lia_poly_norm(const void* in, int ld, const float* coef, void* out, int act_f32, int M, int F, float eps, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(in && coef && out && M > 0 && F > 0 && ld >= F, "lia_poly_norm: bad arguments");
+  if (act_f32) poly_norm_kernel<float><<<M, 256, 0, stream>>>(reinterpret_cast<const float*>(in), ld, coef, reinterpret_cast<float*>(out), F, eps);
+  else poly_norm_kernel<bf16><<<M, 256, 0, stream>>>(reinterpret_cast<const bf16*>(in), ld, coef, reinterpret_cast<bf16*>(out), F, eps);
   LIA_LAUNCH_CHECK();
   return LIA_OK;
 }

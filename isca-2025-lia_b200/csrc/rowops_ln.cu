@@ -4,12 +4,12 @@
 //   ln_add_norm    x += mult * LN_post(y);  x += extra;  h = LN_pre(x)    (each part optional, one pass over the row)
 //   ln_gather      h[r] = LN(x[rows[r]]) for the few rows whose logits are wanted
 //   gated_act      out = act(gate) * up  (or act(gate) alone) on column ranges of one projection's output
-//   router_topk    softmax over the experts' logits, the `top` largest, renormalised
+//   router_topk    softmax over the experts' logits, the `top` largest (by score, or by score plus a correction), renormalised or not
 //   moe_plan       (token, choice) pairs grouped by expert into row tiles
 //   moe_gemm       one projection of every expert over its own rows (gather on the way in, activation or routing weight on
 //                  the way out); moe_fewrows does the same for a handful of pairs with one warp per output
 //   moe_gather     the experts' input rows laid out in the plan's order, for projections that want contiguous rows
-//   moe_combine    y[token] = sum over its choices (+ the shared expert's output)
+//   moe_combine    y[token] = sum over its choices (+ the shared expert's output); identity experts hand the token itself back
 // LN is (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b with fp32 statistics taken in two passes over a staged row.
 #include <math.h>
 
@@ -133,15 +133,17 @@ __global__ void gated_act_kernel(const T* __restrict__ in, int ld, int up_off, T
 }
 
 // ---------------------------------------------------------------------------------------------------- router
-// One warp per token: softmax over E logits (fp32), then `top` rounds of arg-max (lowest index on ties); the chosen
-// scores divided by their sum (+ 1e-20).
-__global__ void __launch_bounds__(128) router_topk_kernel(const float* __restrict__ logits, int* __restrict__ idx, float* __restrict__ wt, int M, int E,
-                                                          int top) {
-  extern __shared__ float sc[];          // [4 warps][E]
+// One warp per token: softmax over E logits (fp32), then `top` rounds of arg-max (lowest index on ties) over the scores
+// plus an optional per-expert correction that takes part in the choice only; the weights are the chosen experts' plain
+// scores, divided by their sum (+ 1e-20) when `renorm` is set.
+__global__ void __launch_bounds__(128) router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int* __restrict__ idx,
+                                                          float* __restrict__ wt, int M, int E, int top, int renorm) {
+  extern __shared__ float sc[];          // [4 warps][2][E]: scores, choice scores
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + warp;
   if (row >= M) return;
-  float* s = sc + warp * E;
+  float* s = sc + warp * 2 * E;
+  float* ch = s + E;
   const float* z = logits + (size_t)row * E;
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
@@ -153,13 +155,17 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restric
     sum += p;
   }
   sum = warp_sum(sum);
+  for (int e = lane; e < E; e += 32) {
+    s[e] = s[e] / sum;
+    ch[e] = s[e] + (correction ? correction[e] : 0.f);
+  }
   __syncwarp();
   float chosen_sum = 0.f;
   for (int t = 0; t < top; ++t) {
-    float best = -1.f;
+    float best = -INFINITY;
     int bi = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
-      const float p = s[e];
+      const float p = ch[e];
       if (p > best) { best = p; bi = e; }          // ascending e: the first of equal scores stays
     }
 #pragma unroll
@@ -168,17 +174,19 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restric
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
     }
-    const float score = best / sum;
+    const float score = s[bi];
     chosen_sum += score;
+    __syncwarp();
     if (lane == 0) {
       idx[(size_t)row * top + t] = bi;
       wt[(size_t)row * top + t] = score;
-      s[bi] = -2.f;                                 // taken
+      ch[bi] = -INFINITY;                           // taken
     }
     __syncwarp();
   }
   __syncwarp();
-  for (int t = lane; t < top; t += 32) wt[(size_t)row * top + t] = wt[(size_t)row * top + t] / (chosen_sum + 1e-20f);
+  if (renorm)
+    for (int t = lane; t < top; t += 32) wt[(size_t)row * top + t] = wt[(size_t)row * top + t] / (chosen_sum + 1e-20f);
 }
 
 // ---------------------------------------------------------------------------------------------------- experts
@@ -220,14 +228,17 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
 //   UP   (gather by token):  src = perm[row] / top,  C = mid[row][n]      = act(sum)
 //   DOWN (rows in place):    src = row,              C = ypair[perm[row]] = wt[perm[row]] * sum     (fp32)
 // 64 x 64 tile, 16-wide k slabs, 4 x 4 outputs per thread, fp32 products and sums in k order (as the plain projection).
-template <typename TA, typename TW, typename TC, bool UP>
+// GATED (UP only): an expert's weights are [2N][K], N gate rows then N up rows, and C = act(gate sum) * (up sum).
+// Tiles of experts >= n_real (experts without weights, whose pairs the combining step serves) are skipped.
+template <typename TA, typename TW, typename TC, bool UP, bool GATED>
 __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ Wt, long long sW, TC* __restrict__ C,
                                                        int ldc, const int* __restrict__ perm, const int* __restrict__ tile_expert,
-                                                       const float* __restrict__ wt, int top, int N, int K, int act) {
+                                                       const float* __restrict__ wt, int top, int N, int K, int act, int n_real) {
   const int e = tile_expert[blockIdx.y];
-  if (e < 0) return;
+  if (e < 0 || e >= n_real) return;
   __shared__ float As[16][TM + 4];
   __shared__ float Ws[16][64 + 4];
+  __shared__ float Wu[GATED ? 16 : 1][64 + 4];
   __shared__ int src[TM], dstp[TM];
   const int row0 = blockIdx.y * TM, n0 = blockIdx.x * 64;
   if (threadIdx.x < TM) {
@@ -238,30 +249,40 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A,
   __syncthreads();
   Wt += (size_t)e * sW;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-  float acc[4][4];
+  float acc[4][4], accu[GATED ? 4 : 1][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < 4; ++j) {
+      acc[i][j] = 0.f;
+      if constexpr (GATED) accu[i][j] = 0.f;
+    }
   for (int k0 = 0; k0 < K; k0 += 16) {
     for (int t = threadIdx.x; t < 64 * 16; t += 256) {
       const int r = t >> 4, kk = t & 15;
       const int k = k0 + kk;
       As[kk][r] = (src[r] >= 0 && k < K) ? ldf(A + (size_t)src[r] * lda + k) : 0.f;
       Ws[kk][r] = (n0 + r < N && k < K) ? ldf(Wt + (size_t)(n0 + r) * K + k) : 0.f;
+      if constexpr (GATED) Wu[kk][r] = (n0 + r < N && k < K) ? ldf(Wt + (size_t)(N + n0 + r) * K + k) : 0.f;
     }
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < 16; ++kk) {
-      float av[4], wv[4];
+      float av[4], wv[4], uv[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) wv[j] = Ws[kk][tx * 4 + j];
+      for (int j = 0; j < 4; ++j) {
+        wv[j] = Ws[kk][tx * 4 + j];
+        if constexpr (GATED) uv[j] = Wu[kk][tx * 4 + j];
+      }
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+        for (int j = 0; j < 4; ++j) {
+          acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+          if constexpr (GATED) accu[i][j] = fmaf(av[i], uv[j], accu[i][j]);
+        }
     }
     __syncthreads();
   }
@@ -274,7 +295,7 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A,
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
       if (n >= N) continue;
-      if (UP) stf(C + (size_t)(row0 + r) * ldc + n, act_apply(acc[i][j], act));
+      if (UP) stf(C + (size_t)(row0 + r) * ldc + n, GATED ? act_apply(acc[i][j], act) * accu[i][j] : act_apply(acc[i][j], act));
       else stf(C + (size_t)p * ldc + n, acc[i][j] * wt[p]);
     }
   }
@@ -301,27 +322,34 @@ __device__ __forceinline__ void load8(const float* p, int k, int K, bool vec, fl
 
 // The same projections for a handful of pairs (decoding): one warp per output n of pair p reads row n of expert idx[p]
 // with 128-bit loads; memory-bound on the chosen experts' weights.  UP: A row = token p / top, C row = p, act applied.
-// DOWN: A row = p, C row = p, times wt[p].
+// DOWN: A row = p, C row = p, times wt[p].  gated (UP): row N + n of the expert is the second factor, C = act(gate) * up.
+// Pairs of experts >= n_real are skipped.
 template <typename TA, typename TW, typename TC, bool UP>
 __global__ void __launch_bounds__(128) moe_fewrows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ Wt, long long sW, TC* __restrict__ C,
                                                           int ldc, const int* __restrict__ idx, const float* __restrict__ wt, int top, int N, int K,
-                                                          int act) {
+                                                          int act, int gated, int n_real) {
   const int p = blockIdx.y, n = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (n >= N) return;
+  if (n >= N || idx[p] >= n_real) return;
   const TW* wr = Wt + (size_t)idx[p] * sW + (size_t)n * K;
   const TA* ar = A + (size_t)(UP ? p / top : p) * lda;
   const bool va = (reinterpret_cast<uintptr_t>(A) % 16 == 0) && ((size_t)lda * sizeof(TA)) % 16 == 0;
   const bool vw = (reinterpret_cast<uintptr_t>(Wt) % 16 == 0) && ((size_t)K * sizeof(TW)) % 16 == 0 && ((size_t)sW * sizeof(TW)) % 16 == 0;
-  float acc = 0.f;
+  float acc = 0.f, accu = 0.f;
   for (int k = lane * 8; k < K; k += 256) {
     float av[8], wv[8];
     load8(ar, k, K, va, av);
     load8(wr, k, K, vw, wv);
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc = fmaf(av[i], wv[i], acc);
+    if (UP && gated) {
+      load8(wr + (size_t)N * K, k, K, vw, wv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) accu = fmaf(av[i], wv[i], accu);
+    }
   }
   acc = warp_sum(acc);
-  if (lane == 0) stf(C + (size_t)p * ldc + n, UP ? act_apply(acc, act) : acc * wt[p]);
+  if (UP && gated) accu = warp_sum(accu);
+  if (lane == 0) stf(C + (size_t)p * ldc + n, UP ? (gated ? act_apply(acc, act) * accu : act_apply(acc, act)) : acc * wt[p]);
 }
 
 // dst[place] = src[perm[place] / top] for every place of the plan, zeros in the padding: the experts' inputs, expert by expert
@@ -337,10 +365,12 @@ __global__ void moe_gather_kernel(const T* __restrict__ src, const int* __restri
 }
 
 // y[m][c] = sum_t f(m * top + t)[c] (in the order of t) + shared[m][c];  f(pair) = ypair[pair], or, with a plan,
-// wt[pair] * ypair[pos_of[pair]] (the experts' outputs still in the plan's order and not yet weighted)
+// wt[pair] * ypair[pos_of[pair]] (the experts' outputs still in the plan's order and not yet weighted).  A pair whose expert
+// idx[pair] >= n_real is an identity expert: f(pair) = wt[pair] * h[m], and ypair is not read for it.
 template <typename TY, typename TS>
 __global__ void moe_combine_kernel(const TY* __restrict__ ypair, const int* __restrict__ pos_of, const float* __restrict__ wt,
-                                   const TS* __restrict__ shared, float* __restrict__ y, int M, int W, int top) {
+                                   const TS* __restrict__ shared, float* __restrict__ y, int M, int W, int top, const int* __restrict__ idx,
+                                   int n_real, const TS* __restrict__ h) {
   const size_t n = (size_t)M * W;
   for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
     const size_t m = e / W;
@@ -348,7 +378,8 @@ __global__ void moe_combine_kernel(const TY* __restrict__ ypair, const int* __re
     float s = 0.f;
     for (int t = 0; t < top; ++t) {
       const size_t pair = m * top + t;
-      if (pos_of) s = fmaf(wt[pair], ldf(ypair + (size_t)pos_of[pair] * W + c), s);
+      if (idx && idx[pair] >= n_real) s = fmaf(wt[pair], ldf(h + e), s);
+      else if (pos_of) s = fmaf(wt[pair], ldf(ypair + (size_t)pos_of[pair] * W + c), s);
       else s += ldf(ypair + pair * W + c);
     }
     if (shared) s += ldf(shared + e);
@@ -425,9 +456,14 @@ extern "C" int lia_gated_act(const void* in, int ld, int up_off, void* out, int 
 }
 
 extern "C" int lia_router_topk(const float* logits, int* idx, float* wt, int M, int E, int top, lia_stream_t stream_) {
+  return lia_router_topk_ext(logits, nullptr, 1, idx, wt, M, E, top, stream_);
+}
+
+extern "C" int lia_router_topk_ext(const float* logits, const float* correction, int renorm, int* idx, float* wt, int M, int E, int top,
+                                   lia_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LIA_CHECK_ARG(logits && idx && wt && M > 0 && E > 0 && top > 0 && top <= E && E <= 2048, "lia_router_topk: bad arguments (E=%d top=%d)", E, top);
-  router_topk_kernel<<<(M + 3) / 4, 128, (size_t)4 * E * sizeof(float), stream>>>(logits, idx, wt, M, E, top);
+  router_topk_kernel<<<(M + 3) / 4, 128, (size_t)8 * E * sizeof(float), stream>>>(logits, correction, idx, wt, M, E, top, renorm);
   LIA_LAUNCH_CHECK();
   return LIA_OK;
 }
@@ -449,32 +485,44 @@ extern "C" int lia_moe_plan(const int* idx, int pairs, int E, int n_tiles, int* 
 extern "C" int lia_moe_gemm(const void* A, int a_f32, int lda, const void* W, int w_f32, long long w_expert_stride, void* C, int c_f32, int ldc,
                             const int* perm, const int* tile_expert, int n_tiles, const int* idx, const float* wt, int pairs, int top, int N,
                             int K, int up, int act, lia_stream_t stream_) {
+  return lia_moe_gemm_ext(A, a_f32, lda, W, w_f32, w_expert_stride, C, c_f32, ldc, perm, tile_expert, n_tiles, idx, wt, pairs, top, N, K, up, act, 0,
+                          0x7fffffff, stream_);
+}
+
+extern "C" int lia_moe_gemm_ext(const void* A, int a_f32, int lda, const void* W, int w_f32, long long w_expert_stride, void* C, int c_f32, int ldc,
+                                const int* perm, const int* tile_expert, int n_tiles, const int* idx, const float* wt, int pairs, int top, int N,
+                                int K, int up, int act, int gated, int n_real, lia_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LIA_CHECK_ARG(A && W && C && idx && wt && pairs > 0 && top > 0 && N > 0 && K > 0 && lda >= K && ldc >= N, "lia_moe_gemm: bad arguments");
+  LIA_CHECK_ARG(!gated || up, "lia_moe_gemm: only the up projection can be gated");
   LIA_CHECK_ARG(a_f32 == w_f32, "lia_moe_gemm: activations and weights must have one type");
   LIA_CHECK_ARG(up ? c_f32 == a_f32 : c_f32 == 1, "lia_moe_gemm: the up projection writes the activations' type, the down projection fp32");
   if (perm == nullptr) {
     LIA_CHECK_ARG(pairs <= 65535, "lia_moe_gemm: too many pairs for the few-rows form");
     dim3 grid((N + 3) / 4, pairs);
     if (a_f32) {
-      if (up) moe_fewrows_kernel<float, float, float, true><<<grid, 128, 0, stream>>>((const float*)A, lda, (const float*)W, w_expert_stride, (float*)C, ldc, idx, wt, top, N, K, act);
-      else moe_fewrows_kernel<float, float, float, false><<<grid, 128, 0, stream>>>((const float*)A, lda, (const float*)W, w_expert_stride, (float*)C, ldc, idx, wt, top, N, K, act);
+      if (up) moe_fewrows_kernel<float, float, float, true><<<grid, 128, 0, stream>>>((const float*)A, lda, (const float*)W, w_expert_stride, (float*)C, ldc, idx, wt, top, N, K, act, gated, n_real);
+      else moe_fewrows_kernel<float, float, float, false><<<grid, 128, 0, stream>>>((const float*)A, lda, (const float*)W, w_expert_stride, (float*)C, ldc, idx, wt, top, N, K, act, gated, n_real);
     } else {
-      if (up) moe_fewrows_kernel<bf16, bf16, bf16, true><<<grid, 128, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, w_expert_stride, (bf16*)C, ldc, idx, wt, top, N, K, act);
-      else moe_fewrows_kernel<bf16, bf16, float, false><<<grid, 128, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, w_expert_stride, (float*)C, ldc, idx, wt, top, N, K, act);
+      if (up) moe_fewrows_kernel<bf16, bf16, bf16, true><<<grid, 128, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, w_expert_stride, (bf16*)C, ldc, idx, wt, top, N, K, act, gated, n_real);
+      else moe_fewrows_kernel<bf16, bf16, float, false><<<grid, 128, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, w_expert_stride, (float*)C, ldc, idx, wt, top, N, K, act, gated, n_real);
     }
     LIA_LAUNCH_CHECK();
     return LIA_OK;
   }
   LIA_CHECK_ARG(tile_expert && n_tiles > 0 && n_tiles <= 65535, "lia_moe_gemm: bad tile plan");
   dim3 grid((N + 63) / 64, n_tiles);
+#define LIA_MG(TA, TC, UP_, GATED_) moe_gemm_kernel<TA, TA, TC, UP_, GATED_><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TA*)W, w_expert_stride, (TC*)C, ldc, perm, tile_expert, wt, top, N, K, act, n_real)
   if (a_f32) {
-    if (up) moe_gemm_kernel<float, float, float, true><<<grid, 256, 0, stream>>>((const float*)A, lda, (const float*)W, w_expert_stride, (float*)C, ldc, perm, tile_expert, wt, top, N, K, act);
-    else moe_gemm_kernel<float, float, float, false><<<grid, 256, 0, stream>>>((const float*)A, lda, (const float*)W, w_expert_stride, (float*)C, ldc, perm, tile_expert, wt, top, N, K, act);
+    if (up && gated) LIA_MG(float, float, true, true);
+    else if (up) LIA_MG(float, float, true, false);
+    else LIA_MG(float, float, false, false);
   } else {
-    if (up) moe_gemm_kernel<bf16, bf16, bf16, true><<<grid, 256, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, w_expert_stride, (bf16*)C, ldc, perm, tile_expert, wt, top, N, K, act);
-    else moe_gemm_kernel<bf16, bf16, float, false><<<grid, 256, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, w_expert_stride, (float*)C, ldc, perm, tile_expert, wt, top, N, K, act);
+    if (up && gated) LIA_MG(bf16, bf16, true, true);
+    else if (up) LIA_MG(bf16, bf16, true, false);
+    else LIA_MG(bf16, float, false, false);
   }
+#undef LIA_MG
   LIA_LAUNCH_CHECK();
   return LIA_OK;
 }
@@ -511,13 +559,19 @@ extern "C" int lia_moe_expert_gemms(const void* A, const void* W, long long w_ex
 
 extern "C" int lia_moe_combine(const void* ypair, int ypair_f32, const int* pos_of, const float* wt, const void* shared, int shared_f32, float* y,
                                int M, int W, int top, lia_stream_t stream_) {
+  return lia_moe_combine_ext(ypair, ypair_f32, pos_of, wt, shared, shared_f32, nullptr, 0, nullptr, y, M, W, top, stream_);
+}
+
+extern "C" int lia_moe_combine_ext(const void* ypair, int ypair_f32, const int* pos_of, const float* wt, const void* shared, int act_f32,
+                                   const int* idx, int n_real, const void* h, float* y, int M, int W, int top, lia_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LIA_CHECK_ARG(ypair && y && M > 0 && W > 0 && top > 0 && (!pos_of || wt), "lia_moe_combine: bad arguments");
+  LIA_CHECK_ARG(!idx || (h && wt && n_real >= 0), "lia_moe_combine: identity experts need the routing weights and the experts' input");
   const unsigned blocks = capped_blocks((size_t)M * W);
-#define LIA_MC(TY, TS) moe_combine_kernel<TY, TS><<<blocks, 256, 0, stream>>>(reinterpret_cast<const TY*>(ypair), pos_of, wt, reinterpret_cast<const TS*>(shared), y, M, W, top)
-  if (ypair_f32 && shared_f32) LIA_MC(float, float);
+#define LIA_MC(TY, TS) moe_combine_kernel<TY, TS><<<blocks, 256, 0, stream>>>(reinterpret_cast<const TY*>(ypair), pos_of, wt, reinterpret_cast<const TS*>(shared), y, M, W, top, idx, n_real, reinterpret_cast<const TS*>(h))
+  if (ypair_f32 && act_f32) LIA_MC(float, float);
   else if (ypair_f32) LIA_MC(float, bf16);
-  else if (shared_f32) LIA_MC(bf16, float);
+  else if (act_f32) LIA_MC(bf16, float);
   else LIA_MC(bf16, bf16);
 #undef LIA_MC
   LIA_LAUNCH_CHECK();

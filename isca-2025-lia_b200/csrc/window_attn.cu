@@ -1,15 +1,24 @@
-// Softmax attention over a sliding window of cached keys and values, with grouped key/value heads, a per-head temperature
-// and a tanh soft cap on the scores; no positional rotation (positions enter only through the window).
+// Softmax attention over a sliding window of cached keys and values (or over the whole history), with grouped key/value
+// heads, a per-head temperature, a tanh soft cap on the scores, a per-head distance bias, a per-head sink in the softmax's
+// denominator and an output gate; the kernel itself rotates nothing (a caller that wants rotated queries and keys hands
+// them in rotated).
 //
 //   kv_store:     the new tokens' keys go into the key cache as they are; each value head is divided by its root mean square
 //                 (fp32) and cached so.
 //   window_attn:  one block per (group of token rows, group of up to 8 query heads, range of keys); a warp owns (row, head)
 //                 pairs.  32 cached positions at a time are staged in shared memory as fp32 for the key/value heads the
 //                 block's query heads use, once for all rows of the block that continue one sequence; lane j scores key j,
-//                     s = cap * tanh((q . k) * scale * temp_h / cap)        (cap <= 0: no cap)
+//                     s = cap * tanh((q . k) * scale * temp_h / cap) - slope_h * (pos - j)     (cap <= 0: no cap)
 //                 over the positions j with 0 <= pos - j < window, folds the stage into a running softmax and accumulates the
-//                 values (lane l owns channels l, l + 32, ...).  Scores, weights and sums are fp32.  Few rows and a long
-//                 window (decoding): the keys are split over several blocks and a second kernel combines.
+//                 values (lane l owns channels l, l + 32, ...).  With a sink the denominator also holds exp(sink_h), a term
+//                 without key or value.  The output can be multiplied by a gate, one number per (row, head) or sigmoid of
+//                 one pre-activation per channel.  Scores, weights and sums are fp32; the queries may be fp32 while the
+//                 caches are bf16.  Few rows and a long window (decoding): the keys are split over several blocks and a
+//                 second kernel combines.
+//   qkv_prep:     what turns a projection's q | k | v columns into attention inputs, per token: bias, a short causal
+//                 convolution over time per channel, an RMS norm of q and of k (over the whole projection or per head), a
+//                 position-dependent query temperature, a rotation of channel pairs, a blend of the values with the values
+//                 that an earlier layer published for the same token; q goes out in fp32, k and v into the caches.
 #include <math.h>
 
 #include "common.cuh"
@@ -49,6 +58,121 @@ __global__ void __launch_bounds__(128) kv_store_kernel(const T* __restrict__ k, 
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------- attention inputs
+struct PrepArgs {
+  int H, G, dim, vdim;
+  int q_off, k_off, v_off;       // columns of q | k | v in a row of the projection's output
+  int taps;                      // 1: no convolution
+  int norm_mode;                 // 0 none; 1 one RMS norm over all of q (and all of k), weights [H*dim], [G*dim]; 2 per head, weights [dim]
+  int temp_every;                // > 0: q *= 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)
+  int rot_dims, rot_halves;      // channels (2i, 2i+1), i < rot_dims/2, of every head turn by pos * freq[i]; rot_halves != 0: pairs (i, i + rot_dims/2)
+  int vmix_mode;                 // 0 none; 1 publish v into v_first; 2 v = (1 - lambda) v + lambda v_first
+  float eps, temp_coef, rot_mag, lambda;
+};
+
+// Block per token row; meta[row] = {slot, position}; rows of one portion are consecutive and so are their positions.
+// conv_state [slot][taps-1][C] holds the projection's outputs (without bias) of the taps - 1 positions before the portion;
+// what lies before the sequence's start counts as zero (no bias either).
+template <typename T>
+__global__ void __launch_bounds__(256) qkv_prep_kernel(const T* __restrict__ y, int ld, const float* __restrict__ bias, const float* __restrict__ wconv,
+                                                       const float* __restrict__ conv_state, const float* __restrict__ qnorm_w,
+                                                       const float* __restrict__ knorm_w, const double* __restrict__ freq, const int* __restrict__ meta,
+                                                       float* __restrict__ v_first, float* __restrict__ q_out, T* __restrict__ kcache,
+                                                       long long k_slot_stride, T* __restrict__ vcache, long long v_slot_stride, PrepArgs a) {
+  extern __shared__ float ch[];                 // C channels q | k | v, then cos | sin of the rotation's pairs
+  __shared__ float red[8];
+  const int row = blockIdx.x;
+  const int slot = meta[2 * row], pos = meta[2 * row + 1];
+  const int nq = a.H * a.dim, nk = a.G * a.dim, nv = a.G * a.vdim, C = nq + nk + nv;
+  float* cs = ch + C;
+  const int npair = a.rot_dims / 2;
+  for (int i = threadIdx.x; i < npair; i += 256) {
+    double s, c;
+    sincos((double)pos * freq[i], &s, &c);      // the angle in full: positions in the thousands times an irrational frequency
+    cs[i] = (float)c * a.rot_mag;
+    cs[npair + i] = (float)s * a.rot_mag;
+  }
+  int inside = 1;                               // rows row-1 .. row-(inside-1) belong to this portion
+  while (inside < a.taps && row - inside >= 0 && meta[2 * (row - inside)] == slot && meta[2 * (row - inside) + 1] == pos - inside) ++inside;
+  const float* st = conv_state ? conv_state + (size_t)slot * (a.taps - 1) * C : nullptr;
+  for (int c = threadIdx.x; c < C; c += 256) {
+    const int col = c < nq ? a.q_off + c : (c < nq + nk ? a.k_off + (c - nq) : a.v_off + (c - nq - nk));
+    const float b = bias ? bias[c] : 0.f;
+    float acc;
+    if (a.taps > 1) {
+      acc = 0.f;
+      for (int j = 0; j < a.taps && j <= pos; ++j) {          // j tokens back
+        const float xin = j < inside ? ldf(y + (size_t)(row - j) * ld + col) : st[(size_t)(inside - 1 - j + a.taps - 1) * C + c];
+        acc = fmaf(wconv[(size_t)c * a.taps + a.taps - 1 - j], xin + b, acc);
+      }
+    } else {
+      acc = ldf(y + (size_t)row * ld + col) + b;
+    }
+    ch[c] = acc;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float temp = 1.0f;
+  if (a.temp_every > 0) temp = 1.0f + a.temp_coef * logf((float)((pos + 1) / a.temp_every) + 1.0f);
+  if (a.norm_mode == 1) {
+    float sq = 0.f, sk = 0.f;
+    for (int c = threadIdx.x; c < nq; c += 256) sq += ch[c] * ch[c];
+    for (int c = nq + threadIdx.x; c < nq + nk; c += 256) sk += ch[c] * ch[c];
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if (lane == 0) red[warp] = sq;
+    __syncthreads();
+    float tq = 0.f;
+    for (int w = 0; w < 8; ++w) tq += red[w];
+    __syncthreads();
+    if (lane == 0) red[warp] = sk;
+    __syncthreads();
+    float tk = 0.f;
+    for (int w = 0; w < 8; ++w) tk += red[w];
+    const float iq = temp / sqrtf(tq / (float)nq + a.eps), ik = 1.0f / sqrtf(tk / (float)nk + a.eps);
+    for (int c = threadIdx.x; c < nq; c += 256) ch[c] *= iq * qnorm_w[c];
+    for (int c = threadIdx.x; c < nk; c += 256) ch[nq + c] *= ik * knorm_w[c];
+  } else {
+    for (int hd = warp; hd < a.H + a.G; hd += 8) {            // q heads, then k heads
+      float* hv = ch + hd * a.dim;
+      const bool is_q = hd < a.H;
+      float inv = is_q ? temp : 1.0f;
+      if (a.norm_mode == 2) {
+        float ss = 0.f;
+        for (int i = lane; i < a.dim; i += 32) ss += hv[i] * hv[i];
+        inv /= sqrtf(warp_sum(ss) / (float)a.dim + a.eps);
+      }
+      const float* w = a.norm_mode == 2 ? (is_q ? qnorm_w : knorm_w) : nullptr;
+      for (int i = lane; i < a.dim; i += 32) hv[i] *= inv * (w ? w[i] : 1.0f);
+    }
+  }
+  __syncthreads();
+  // rotation and the way out: q in fp32, k into the cache
+  T* kr = kcache + (size_t)slot * k_slot_stride + (size_t)pos * nk;
+  for (int e = threadIdx.x; e < nq + nk; e += 256) {
+    const int hd = e / a.dim, i = e - hd * a.dim;
+    float val = ch[e];
+    if (i < a.rot_dims) {
+      int p, mate;
+      bool first;
+      if (a.rot_halves) { first = i < npair; p = first ? i : i - npair; mate = first ? i + npair : i - npair; }
+      else { first = (i & 1) == 0; p = i >> 1; mate = i ^ 1; }
+      const float other = ch[hd * a.dim + mate];
+      val = first ? val * cs[p] - other * cs[npair + p] : val * cs[p] + other * cs[npair + p];
+    }
+    if (e < nq) q_out[(size_t)row * nq + e] = val;
+    else stf(kr + (e - nq), val);
+  }
+  T* vr = vcache + (size_t)slot * v_slot_stride + (size_t)pos * nv;
+  for (int c = threadIdx.x; c < nv; c += 256) {
+    float val = ch[nq + nk + c];
+    if (a.vmix_mode == 1) v_first[(size_t)row * nv + c] = val;
+    else if (a.vmix_mode == 2) val = (1.0f - a.lambda) * val + a.lambda * v_first[(size_t)row * nv + c];
+    stf(vr + c, val);
+  }
+}
+
 constexpr int TK = 32;     // cached positions per stage (= lanes: lane j scores key j)
 constexpr int NWARP = 8;
 
@@ -56,7 +180,23 @@ struct WindowArgs {
   int H, G, dim, vdim, window;
   int HB, NG, QR, nsplit;      // query heads per block (spanning at most NG key/value heads), rows per block, key ranges per row
   float scale, softcap;
+  int q_f32, gate_mode, ldg;   // queries in fp32; gate: 0 none, 1 fp32 [M][H] as is, 2 sigmoid of the activations' type [M][ldg], per channel
 };
+
+// what the scores and the output take besides q, k, v (each may be null)
+struct WindowExtras {
+  const float* temp;     // [H] multiplies the scaled score
+  const float* slopes;   // [H] slope_h * (pos - j) is taken off the score
+  const float* sink;     // [H] exp(sink_h) joins the softmax's denominator
+  const void* gate;      // see WindowArgs::gate_mode
+};
+
+template <typename T>
+__device__ __forceinline__ float gate_of(const WindowExtras& x, const WindowArgs& a, size_t row, int h, int ch) {
+  if (a.gate_mode == 1) return reinterpret_cast<const float*>(x.gate)[row * a.H + h];
+  if (a.gate_mode == 2) return 1.0f / (1.0f + expf(-ldf(reinterpret_cast<const T*>(x.gate) + row * a.ldg + (size_t)h * a.vdim + ch)));
+  return 1.0f;
+}
 
 __host__ __device__ inline int key_stride(int dim) { return dim % 4 == 0 ? dim + 4 : (dim | 1); }   // conflict-free rows (128-bit or scalar reads)
 
@@ -105,9 +245,9 @@ __device__ __forceinline__ void stage_rows(const T* __restrict__ cache, int G, i
 // keeps its running maximum, sum and value accumulators (lane l: channels l, l + 32, ...) in registers; PP pairs per warp.
 // nsplit > 1: unnormalised sums to `part` [M][H][nsplit][vdim] and (max, sum) to `part_ml`; window_combine_kernel finishes.
 template <typename T, int VR, int PP>
-__global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ kcache, long long k_slot_stride,
+__global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const void* __restrict__ q, int ldq, const T* __restrict__ kcache, long long k_slot_stride,
                                                                 const T* __restrict__ vcache, long long v_slot_stride, const int* __restrict__ meta,
-                                                                const float* __restrict__ temp, T* __restrict__ out, float* __restrict__ part,
+                                                                WindowExtras x, T* __restrict__ out, float* __restrict__ part,
                                                                 float2* __restrict__ part_ml, int M, WindowArgs a) {
   extern __shared__ __align__(16) float sm[];
   const int DKS = key_stride(a.dim);
@@ -138,7 +278,8 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const T* __rest
     for (int e = threadIdx.x; e < npairs * a.dim; e += NWARP * 32) {
       const int p = e / a.dim, d = e - p * a.dim;
       const int i = p / nh, hh = p - i * nh;
-      qs[e] = ldf(q + (size_t)(r + i) * ldq + (size_t)(h0 + hh) * a.dim + d);
+      const size_t at = (size_t)(r + i) * ldq + (size_t)(h0 + hh) * a.dim + d;
+      qs[e] = a.q_f32 ? reinterpret_cast<const float*>(q)[at] : ldf(reinterpret_cast<const T*>(q) + at);
     }
     float m_run[PP], l_run[PP], acc[PP][VR];
 #pragma unroll
@@ -161,7 +302,8 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const T* __rest
         // All pairs of this warp are rows of ONE query head (nh divides the warp count): a staged key or value row is read
         // from shared memory once and serves the PP rows.
         const int hh = warp % nh, h = h0 + hh, gi = h / rep - g_lo;
-        const float sc_mul = a.scale * temp[h];
+        const float sc_mul = a.scale * (x.temp ? x.temp[h] : 1.0f);
+        const float slope = x.slopes ? x.slopes[h] : 0.f;
         bool active[PP];
         int lo_min = 0x7fffffff, pos_max = -1;
 #pragma unroll
@@ -205,6 +347,7 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const T* __rest
             float sc = dot[s] * sc_mul;
             if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
             const int j = j0 + lane;
+            sc -= slope * (float)(pos - j);
             if (lane >= nk || j < lo || j > pos) sc = -INFINITY;
             const float m_new = fmaxf(m_run[s], warp_max(sc));  // finite: at least one key of the stage is visible
             pr[s] = expf(sc - m_new);
@@ -254,9 +397,10 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const T* __rest
         } else {
           for (int d = 0; d < a.dim; ++d) dot = fmaf(qr[d], kr[d], dot);
         }
-        float sc = dot * a.scale * temp[h];
+        float sc = dot * a.scale * (x.temp ? x.temp[h] : 1.0f);
         if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
         const int j = j0 + lane;
+        if (x.slopes) sc -= x.slopes[h] * (float)(pos - j);
         if (lane >= nk || j < lo || j > pos) sc = -INFINITY;
         const float m_new = fmaxf(m_run[s], warp_max(sc));      // finite: at least one key of the stage is visible
         const float pr = expf(sc - m_new);
@@ -284,11 +428,11 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const T* __rest
       const int i = p / nh, hh = p - i * nh;
       const size_t rh = (size_t)(r + i) * a.H + h0 + hh;
       if (a.nsplit == 1) {
-        const float invl = 1.0f / l_run[s];
+        const float invl = 1.0f / (l_run[s] + (x.sink ? expf(x.sink[h0 + hh] - m_run[s]) : 0.f));
 #pragma unroll
         for (int c = 0; c < VR; ++c) {
           const int ch = lane + 32 * c;
-          if (ch < a.vdim) stf(out + rh * a.vdim + ch, acc[s][c] * invl);
+          if (ch < a.vdim) stf(out + rh * a.vdim + ch, acc[s][c] * invl * gate_of<T>(x, a, (size_t)(r + i), h0 + hh, ch));
         }
       } else {
 #pragma unroll
@@ -306,8 +450,10 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const T* __rest
 // out[rh] = sum_z part[rh][z] e^(m_z - m) / sum_z l_z e^(m_z - m), m = max_z m_z (a part without visible keys has m = -inf, l = 0)
 template <typename T>
 __global__ void __launch_bounds__(128) window_combine_kernel(const float* __restrict__ part, const float2* __restrict__ part_ml, T* __restrict__ out,
-                                                             int vdim, int nsplit) {
+                                                             int vdim, int nsplit, WindowExtras x, WindowArgs a) {
   const size_t rh = blockIdx.x;
+  const int h = (int)(rh % a.H);
+  const size_t row = rh / a.H;
   float m = -INFINITY;
   for (int z = 0; z < nsplit; ++z) m = fmaxf(m, part_ml[rh * nsplit + z].x);
   float l = 0.f;
@@ -315,6 +461,7 @@ __global__ void __launch_bounds__(128) window_combine_kernel(const float* __rest
     const float2 ml = part_ml[rh * nsplit + z];
     if (ml.y > 0.f) l += ml.y * expf(ml.x - m);
   }
+  if (x.sink) l += expf(x.sink[h] - m);
   const float invl = 1.0f / l;
   for (int c = threadIdx.x; c < vdim; c += 128) {
     float s = 0.f;
@@ -322,7 +469,7 @@ __global__ void __launch_bounds__(128) window_combine_kernel(const float* __rest
       const float2 ml = part_ml[rh * nsplit + z];
       if (ml.y > 0.f) s = fmaf(part[(rh * nsplit + z) * vdim + c], expf(ml.x - m), s);
     }
-    stf(out + rh * vdim + c, s * invl);
+    stf(out + rh * vdim + c, s * invl * gate_of<T>(x, a, row, h, c));
   }
 }
 
@@ -331,7 +478,7 @@ size_t attn_smem(const WindowArgs& a) {
 }
 
 template <typename T, int VR, int PP>
-int launch_attn(const void* q, int ldq, const void* kcache, long long kss, const void* vcache, long long vss, const int* meta, const float* temp,
+int launch_attn(const void* q, int ldq, const void* kcache, long long kss, const void* vcache, long long vss, const int* meta, const WindowExtras& x,
                 void* out, float* ws, int M, const WindowArgs& a, cudaStream_t stream) {
   LIA_CHECK_ARG((a.QR * a.HB + NWARP - 1) / NWARP <= PP, "lia_window_attn: %d rows x %d heads per block are too many for value heads of %d", a.QR, a.HB, a.vdim);
   const size_t smem = attn_smem(a);
@@ -339,19 +486,19 @@ int launch_attn(const void* q, int ldq, const void* kcache, long long kss, const
   dim3 grid((M + a.QR - 1) / a.QR, (a.H + a.HB - 1) / a.HB, a.nsplit);
   float* part = ws;
   float2* part_ml = reinterpret_cast<float2*>(ws + (size_t)M * a.H * a.nsplit * a.vdim);
-  window_attn_kernel<T, VR, PP><<<grid, NWARP * 32, smem, stream>>>(reinterpret_cast<const T*>(q), ldq, reinterpret_cast<const T*>(kcache), kss,
-                                                                   reinterpret_cast<const T*>(vcache), vss, meta, temp, reinterpret_cast<T*>(out), part,
+  window_attn_kernel<T, VR, PP><<<grid, NWARP * 32, smem, stream>>>(q, ldq, reinterpret_cast<const T*>(kcache), kss,
+                                                                   reinterpret_cast<const T*>(vcache), vss, meta, x, reinterpret_cast<T*>(out), part,
                                                                    part_ml, M, a);
   LIA_LAUNCH_CHECK();
   if (a.nsplit > 1) {
-    window_combine_kernel<T><<<(unsigned)((size_t)M * a.H), 128, 0, stream>>>(part, part_ml, reinterpret_cast<T*>(out), a.vdim, a.nsplit);
+    window_combine_kernel<T><<<(unsigned)((size_t)M * a.H), 128, 0, stream>>>(part, part_ml, reinterpret_cast<T*>(out), a.vdim, a.nsplit, x, a);
     LIA_LAUNCH_CHECK();
   }
   return LIA_OK;
 }
 
 template <typename T>
-int dispatch_attn(const void* q, int ldq, const void* kcache, long long kss, const void* vcache, long long vss, const int* meta, const float* temp,
+int dispatch_attn(const void* q, int ldq, const void* kcache, long long kss, const void* vcache, long long vss, const int* meta, const WindowExtras& temp,
                   void* out, float* ws, int M, const WindowArgs& a, cudaStream_t stream) {
   if (a.vdim <= 32) return launch_attn<T, 1, 4>(q, ldq, kcache, kss, vcache, vss, meta, temp, out, ws, M, a, stream);
   if (a.vdim <= 64) return launch_attn<T, 2, 4>(q, ldq, kcache, kss, vcache, vss, meta, temp, out, ws, M, a, stream);
@@ -377,6 +524,35 @@ extern "C" int lia_kv_store(const void* k, int ldk, const void* v, int ldv, int 
   return LIA_OK;
 }
 
+/* see lia_b200.h */
+extern "C" int lia_qkv_prep(const void* y, int act_f32, int ld, int q_off, int k_off, int v_off, const float* bias, const float* wconv,
+                            const float* conv_state, int taps, int norm_mode, const float* qnorm_w, const float* knorm_w, float eps,
+                            float temp_coef, int temp_every, const double* freq, int rot_dims, int rot_halves, float rot_mag, int vmix_mode,
+                            float lambda, float* v_first, const int* meta, float* q_out, void* kcache, long long k_slot_stride, void* vcache,
+                            long long v_slot_stride, int M, int H, int G, int dim, int vdim, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(y && meta && q_out && kcache && vcache, "lia_qkv_prep: null pointer");
+  LIA_CHECK_ARG(M > 0 && H > 0 && G > 0 && dim > 0 && vdim > 0 && taps >= 1 && taps <= 8 && (taps == 1 || (wconv && conv_state)),
+                "lia_qkv_prep: bad shape H=%d G=%d dim=%d vdim=%d taps=%d", H, G, dim, vdim, taps);
+  LIA_CHECK_ARG(norm_mode >= 0 && norm_mode <= 2 && (norm_mode == 0 || (qnorm_w && knorm_w)), "lia_qkv_prep: bad norm mode %d", norm_mode);
+  LIA_CHECK_ARG(rot_dims >= 0 && rot_dims <= dim && rot_dims % 2 == 0 && (rot_dims == 0 || freq), "lia_qkv_prep: cannot rotate %d of %d channels", rot_dims, dim);
+  LIA_CHECK_ARG(vmix_mode >= 0 && vmix_mode <= 2 && (vmix_mode == 0 || v_first), "lia_qkv_prep: bad value-mixing mode %d", vmix_mode);
+  PrepArgs a{H, G, dim, vdim, q_off, k_off, v_off, taps, norm_mode, temp_every, rot_dims, rot_halves, vmix_mode, eps, temp_coef, rot_mag, lambda};
+  const size_t smem = ((size_t)(H + G) * dim + (size_t)G * vdim + rot_dims) * sizeof(float);
+  LIA_CHECK_ARG(smem <= 160 * 1024, "lia_qkv_prep: %d channels do not fit shared memory", (H + G) * dim + G * vdim);
+  if (act_f32) {
+    if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(qkv_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    qkv_prep_kernel<float><<<M, 256, smem, stream>>>(reinterpret_cast<const float*>(y), ld, bias, wconv, conv_state, qnorm_w, knorm_w, freq, meta, v_first,
+                                                     q_out, reinterpret_cast<float*>(kcache), k_slot_stride, reinterpret_cast<float*>(vcache), v_slot_stride, a);
+  } else {
+    if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(qkv_prep_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    qkv_prep_kernel<bf16><<<M, 256, smem, stream>>>(reinterpret_cast<const bf16*>(y), ld, bias, wconv, conv_state, qnorm_w, knorm_w, freq, meta, v_first,
+                                                    q_out, reinterpret_cast<bf16*>(kcache), k_slot_stride, reinterpret_cast<bf16*>(vcache), v_slot_stride, a);
+  }
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
 // Pairs (row, head) that one warp can carry for value heads of `vdim` numbers: bounds rows_per_block * heads_per_block / 8.
 extern "C" int lia_window_attn_pairs_per_warp(int vdim) { return vdim <= 128 ? 4 : (vdim <= 256 ? 2 : 1); }
 
@@ -390,19 +566,33 @@ extern "C" size_t lia_window_attn_workspace_floats(int M, int H, int vdim, int n
   return (size_t)M * H * nsplit * ((size_t)vdim + 2);
 }
 
+extern "C" int lia_window_attn_ext(const void* q, int ldq, int q_f32, int act_f32, const void* kcache, long long k_slot_stride, const void* vcache,
+                                   long long v_slot_stride, const int* meta, const float* temp, const float* slopes, const float* sink,
+                                   const void* gate, int gate_mode, int ldg, void* out, float* workspace, int M, int H, int G, int dim, int vdim,
+                                   int window, float scale, float softcap, int heads_per_block, int rows_per_block, int nsplit,
+                                   lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(q && kcache && vcache && meta && out, "lia_window_attn: null pointer");
+  LIA_CHECK_ARG(M > 0 && H > 0 && G > 0 && H % G == 0 && dim > 0 && vdim > 0 && vdim <= 512 && H <= 65535 && ldq >= H * dim,
+                "lia_window_attn: bad shape H=%d G=%d dim=%d vdim=%d window=%d", H, G, dim, vdim, window);
+  LIA_CHECK_ARG(gate_mode >= 0 && gate_mode <= 2 && (gate_mode == 0) == (gate == nullptr) && (gate_mode != 2 || ldg >= H * vdim),
+                "lia_window_attn: bad output gate (mode %d, row stride %d)", gate_mode, ldg);
+  if (window <= 0) window = 1 << 30;                             // the whole history
+  const int rep = H / G, HB = heads_per_block;
+  LIA_CHECK_ARG(HB >= 1 && HB <= NWARP && (HB % rep == 0 || rep % HB == 0), "lia_window_attn: %d heads per block do not fit groups of %d", HB, rep);
+  LIA_CHECK_ARG(rows_per_block >= 1 && nsplit >= 1 && nsplit <= 64 && (nsplit == 1 || workspace), "lia_window_attn: bad rows per block (%d) or key ranges (%d)", rows_per_block, nsplit);
+  WindowArgs a{H, G, dim, vdim, window, HB, HB >= rep ? HB / rep : 1, rows_per_block, nsplit, scale, softcap, q_f32 || act_f32, gate_mode, ldg};
+  LIA_CHECK_ARG(attn_smem(a) <= 200 * 1024, "lia_window_attn: heads of %d + %d numbers do not fit the shared-memory stage", dim, vdim);
+  const WindowExtras x{temp, slopes, sink, gate};
+  if (act_f32) return dispatch_attn<float>(q, ldq, kcache, k_slot_stride, vcache, v_slot_stride, meta, x, out, workspace, M, a, stream);
+  return dispatch_attn<bf16>(q, ldq, kcache, k_slot_stride, vcache, v_slot_stride, meta, x, out, workspace, M, a, stream);
+}
+
 extern "C" int lia_window_attn(const void* q, int ldq, int act_f32, const void* kcache, long long k_slot_stride, const void* vcache,
                                long long v_slot_stride, const int* meta, const float* temp, void* out, float* workspace, int M, int H, int G,
                                int dim, int vdim, int window, float scale, float softcap, int heads_per_block, int rows_per_block, int nsplit,
                                lia_stream_t stream_) {
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  LIA_CHECK_ARG(q && kcache && vcache && meta && temp && out, "lia_window_attn: null pointer");
-  LIA_CHECK_ARG(M > 0 && H > 0 && G > 0 && H % G == 0 && dim > 0 && vdim > 0 && vdim <= 512 && window > 0 && H <= 65535 && ldq >= H * dim,
-                "lia_window_attn: bad shape H=%d G=%d dim=%d vdim=%d window=%d", H, G, dim, vdim, window);
-  const int rep = H / G, HB = heads_per_block;
-  LIA_CHECK_ARG(HB >= 1 && HB <= NWARP && (HB % rep == 0 || rep % HB == 0), "lia_window_attn: %d heads per block do not fit groups of %d", HB, rep);
-  LIA_CHECK_ARG(rows_per_block >= 1 && nsplit >= 1 && nsplit <= 64 && (nsplit == 1 || workspace), "lia_window_attn: bad rows per block (%d) or key ranges (%d)", rows_per_block, nsplit);
-  WindowArgs a{H, G, dim, vdim, window, HB, HB >= rep ? HB / rep : 1, rows_per_block, nsplit, scale, softcap};
-  LIA_CHECK_ARG(attn_smem(a) <= 200 * 1024, "lia_window_attn: heads of %d + %d numbers do not fit the shared-memory stage", dim, vdim);
-  if (act_f32) return dispatch_attn<float>(q, ldq, kcache, k_slot_stride, vcache, v_slot_stride, meta, temp, out, workspace, M, a, stream);
-  return dispatch_attn<bf16>(q, ldq, kcache, k_slot_stride, vcache, v_slot_stride, meta, temp, out, workspace, M, a, stream);
+  LIA_CHECK_ARG(temp && window > 0, "lia_window_attn: needs a temperature per head and a positive window");
+  return lia_window_attn_ext(q, ldq, act_f32, act_f32, kcache, k_slot_stride, vcache, v_slot_stride, meta, temp, nullptr, nullptr, nullptr, 0, 0, out,
+                             workspace, M, H, G, dim, vdim, window, scale, softcap, heads_per_block, rows_per_block, nsplit, stream_);
 }

@@ -530,13 +530,16 @@ def gated_act(inp, F, out, act, up_off=-1):
     return out
 
 
-def router_topk(logits, top, idx, wt):
-    """Softmax over the experts, the ``top`` largest scores and their renormalised weights: idx int32 [M, top], wt fp32."""
+def router_topk(logits, top, idx, wt, correction=None, renorm=True):
+    """Softmax over the experts, the ``top`` largest scores and their weights: idx int32 [M, top], wt fp32.  ``correction``
+    [E] is added to the scores for the choice only; ``renorm`` divides the chosen scores by their sum."""
     _req(logits, "logits", F32); _req(idx, "idx", I32); _req(wt, "wt", F32)
     M, E = logits.shape
-    if tuple(idx.shape) != (M, top) or tuple(wt.shape) != (M, top):
-        raise _lib.LiaError("router_topk: idx and wt must be [M, top]")
-    check(_lib.load().lia_router_topk(_p(logits), _p(idx), _p(wt), M, E, top, _stream()), "lia_router_topk")
+    if tuple(idx.shape) != (M, top) or tuple(wt.shape) != (M, top) or (correction is not None and correction.numel() != E):
+        raise _lib.LiaError("router_topk: idx and wt must be [M, top], the correction [E]")
+    if correction is not None:
+        _req(correction, "correction", F32)
+    check(_lib.load().lia_router_topk_ext(_p(logits), _p(correction), int(renorm), _p(idx), _p(wt), M, E, top, _stream()), "lia_router_topk")
     count_launches()
 
 
@@ -552,16 +555,20 @@ def moe_plan(idx, E, perm, tile_expert, pos_of):
     count_launches()
 
 
-def moe_gemm(a, w, out, idx, wt, top, up, act=ACT_NONE, perm=None, tile_expert=None):
+def moe_gemm(a, w, out, idx, wt, top, up, act=ACT_NONE, perm=None, tile_expert=None, gated=False):
     """One projection of every expert over its own rows; ``w`` [E, N, K].  up: out[place] = act(a[token] @ w[e].T);
-    down: out[pair] = wt[pair] * a[place] @ w[e].T (fp32).  Without a plan (``perm`` None) a pair's place is the pair."""
+    down: out[pair] = wt[pair] * a[place] @ w[e].T (fp32).  Without a plan (``perm`` None) a pair's place is the pair.
+    ``gated`` (up only): ``w`` is [E, 2N, K], N gate rows then N up rows, and out = act(gate) * up.  Pairs whose expert
+    index is E or more (experts without weights) are left out."""
     _dev(a, "a"); _dev(w, "w"); _dev(out, "out")
     E, N, K = w.shape
+    if gated:
+        N //= 2
     if not (w.is_contiguous() and a.is_contiguous() and out.is_contiguous() and a.shape[1] == K and out.shape[1] == N):
         raise _lib.LiaError(f"moe_gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    check(_lib.load().lia_moe_gemm(_p(a), _f32(a), K, _p(w), _f32(w), N * K, _p(out), _f32(out), N, _p(perm), _p(tile_expert),
-                                   tile_expert.numel() if tile_expert is not None else 0, _p(idx), _p(wt), idx.numel(), top, N, K, int(up), act,
-                                   _stream()), "lia_moe_gemm")
+    check(_lib.load().lia_moe_gemm_ext(_p(a), _f32(a), K, _p(w), _f32(w), w.stride(0), _p(out), _f32(out), N, _p(perm), _p(tile_expert),
+                                       tile_expert.numel() if tile_expert is not None else 0, _p(idx), _p(wt), idx.numel(), top, N, K, int(up), act,
+                                       int(gated), E, _stream()), "lia_moe_gemm")
     count_launches()
     return out
 
@@ -591,17 +598,26 @@ def moe_expert_gemms(a, w, out, tiles_per_expert, tile_rows, workspace):
     return out
 
 
-def moe_combine(ypair, shared, y, top, pos_of=None, wt=None):
+def moe_combine(ypair, shared, y, top, pos_of=None, wt=None, identity=None):
     """y[m] = sum over the token's choices (+ the shared expert's output).  Without a plan ``ypair`` holds the weighted
-    outputs pair by pair; with ``pos_of`` and ``wt`` it holds the unweighted outputs in the plan's order."""
+    outputs pair by pair; with ``pos_of`` and ``wt`` it holds the unweighted outputs in the plan's order.  ``identity`` =
+    (idx, first identity expert, h, wt): a pair routed to an expert from that index on contributes wt * h[m]."""
     _dev(ypair, "ypair"); _req(y, "y", F32)
     M, W = y.shape
     if shared is not None and not (shared.is_contiguous() and tuple(shared.shape) == (M, W)):
         raise _lib.LiaError("moe_combine: the shared expert's output must be a contiguous [M, W] tensor")
     if not ypair.is_contiguous() or ypair.shape[1] != W or (pos_of is None) != (wt is None):
         raise _lib.LiaError("moe_combine: ypair must be a contiguous [.., W] tensor; pos_of and wt go together")
-    check(_lib.load().lia_moe_combine(_p(ypair), _f32(ypair), _p(pos_of), _p(wt), _p(shared), _f32(shared) if shared is not None else 1, _p(y), M, W,
-                                      top, _stream()), "lia_moe_combine")
+    idx, n_real, h = None, 0, None
+    if identity is not None:
+        idx, n_real, h, wt_id = identity
+        _req(idx, "idx", I32); _req(wt_id, "wt", F32)
+        if not (h.is_contiguous() and tuple(h.shape) == (M, W)) or (shared is not None and shared.dtype != h.dtype):
+            raise _lib.LiaError("moe_combine: the experts' input must be a contiguous [M, W] tensor of the shared expert's type")
+        wt = wt_id
+    act = h if h is not None else shared
+    check(_lib.load().lia_moe_combine_ext(_p(ypair), _f32(ypair), _p(pos_of), _p(wt), _p(shared), _f32(act) if act is not None else 1, _p(idx),
+                                          n_real, _p(h), _p(y), M, W, top, _stream()), "lia_moe_combine")
     count_launches()
     return y
 
@@ -622,12 +638,13 @@ def conv_prep(y, offs, wconv, conv_state, meta, gates, a_log, dt_bias, qk, v, G,
     count_launches()
 
 
-def conv_state_update(y, offs, nqk, nv, conv_state, segs, taps):
-    """The last ``taps`` - 1 inputs of every portion become its sequence's convolution state (after ``conv_prep``)."""
+def conv_state_update(y, offs, nqk, nv, conv_state, segs, taps, nk=None):
+    """The last ``taps`` - 1 inputs of every portion become its sequence's convolution state (after ``conv_prep`` or
+    ``qkv_prep``).  ``nqk`` channels of q and ``nk`` of k (None: as many), ``nv`` of v."""
     ld = _rowmajor(y, "y")
     _req(conv_state, "conv_state", F32); _req(segs, "segs", I32)
     if taps > 1:
-        check(_lib.load().lia_conv_state_update(_p(y), _f32(y), ld, offs[0], offs[1], offs[2], nqk, nv, _p(conv_state), _p(segs), segs.shape[0],
+        check(_lib.load().lia_conv_state_update(_p(y), _f32(y), ld, offs[0], offs[1], offs[2], nqk, nqk if nk is None else nk, nv, _p(conv_state), _p(segs), segs.shape[0],
                                                 taps, _stream()), "lia_conv_state_update")
         count_launches()
 
@@ -694,21 +711,117 @@ def window_attn_plan(M, nseg, H, G, dim, vdim, window, max_ctx, sms):
     return hb, qr, nsplit
 
 
-def window_attn(q, kcache, vcache, meta, temp, out, H, G, dim, vdim, window, scale, softcap, nseg=None, max_ctx=0):
-    """Softmax attention of every row over the last ``window`` cached positions of its sequence (csrc/window_attn.cu).
-    ``nseg``: portions in the step (None: one row each); ``max_ctx``: an upper bound of the rows' history lengths (0: unknown,
-    no split of the keys)."""
+def window_attn(q, kcache, vcache, meta, temp, out, H, G, dim, vdim, window, scale, softcap, nseg=None, max_ctx=0, slopes=None, sink=None,
+                gate=None, gate_per_head=False):
+    """Softmax attention of every row over the last ``window`` cached positions of its sequence (csrc/window_attn.cu);
+    ``window`` <= 0: over its whole history.  ``nseg``: portions in the step (None: one row each); ``max_ctx``: an upper
+    bound of the rows' history lengths (0: unknown, no split of the keys).  ``temp`` [H] multiplies the scores, ``slopes``
+    [H] take slope * distance off them, ``sink`` [H] joins the denominator; ``gate`` multiplies the output: fp32 [M, H]
+    as it is (``gate_per_head``), else sigmoid of a pre-activation per channel (a column slice of the activations' type).
+    ``q`` may be fp32 while the caches are bf16."""
     ldq = _rowmajor(q, "q")
-    _req(meta, "meta", I32); _req(temp, "temp", F32)
+    _req(meta, "meta", I32)
+    for t, n in ((temp, "temp"), (slopes, "slopes"), (sink, "sink")):
+        if t is not None and (_req(t, n, F32).numel() != H):
+            raise _lib.LiaError(f"window_attn: {n} must be [H]")
     M = q.shape[0]
-    if not (out.is_contiguous() and tuple(out.shape) == (M, H * vdim) and out.dtype == q.dtype == kcache.dtype == vcache.dtype and temp.numel() == H):
-        raise _lib.LiaError("window_attn: out must be a contiguous [M, H * vdim] tensor of the activations' dtype, temp [H]")
-    hb, qr, nsplit = window_attn_plan(M, nseg if nseg is not None else M, H, G, dim, vdim, int(window), max_ctx, _sm_count(q.device))
+    if not (out.is_contiguous() and tuple(out.shape) == (M, H * vdim) and out.dtype == kcache.dtype == vcache.dtype and q.dtype in (F32, out.dtype)):
+        raise _lib.LiaError("window_attn: out must be a contiguous [M, H * vdim] tensor of the caches' dtype, q of that dtype or fp32")
+    gate_mode, ldg = 0, 0
+    if gate is not None:
+        ldg = _rowmajor(gate, "gate")
+        if gate_per_head:
+            gate_mode = 1
+            if gate.dtype != F32 or tuple(gate.shape) != (M, H) or ldg != H:
+                raise _lib.LiaError("window_attn: a per-head gate must be a contiguous fp32 [M, H] tensor")
+        else:
+            gate_mode = 2
+            if gate.dtype != out.dtype or tuple(gate.shape) != (M, H * vdim):
+                raise _lib.LiaError("window_attn: a per-channel gate must be an [M, H * vdim] slice of the activations' dtype")
+    window = int(window) if window > 0 else 1 << 30
+    hb, qr, nsplit = window_attn_plan(M, nseg if nseg is not None else M, H, G, dim, vdim, window, max_ctx, _sm_count(q.device))
     ws = None
     if nsplit > 1:
         ws = torch.empty(_lib.load().lia_window_attn_workspace_floats(M, H, vdim, nsplit), dtype=F32, device=q.device)
-    check(_lib.load().lia_window_attn(_p(q), ldq, _f32(q), _p(kcache), kcache.stride(0), _p(vcache), vcache.stride(0), _p(meta), _p(temp), _p(out),
-                                      _p(ws), M, H, G, dim, vdim, int(window), float(scale), float(softcap), hb, qr, nsplit, _stream()),
-          "lia_window_attn")
+    check(_lib.load().lia_window_attn_ext(_p(q), ldq, _f32(q), _f32(out), _p(kcache), kcache.stride(0), _p(vcache), vcache.stride(0), _p(meta), _p(temp),
+                                          _p(slopes), _p(sink), _p(gate), gate_mode, ldg, _p(out), _p(ws), M, H, G, dim, vdim, window, float(scale),
+                                          float(softcap), hb, qr, nsplit, _stream()), "lia_window_attn")
     count_launches(2 if nsplit > 1 else 1)
+    return out
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# Models that norm and gate a sublayer's OUTPUT and hand on a weighted mix of all earlier layers' results; attention inputs
+# behind a bias, a short convolution, a norm, a temperature, a rotation and a blend of values.  (Not in the reference either.)
+# ------------------------------------------------------------------------------------------------------------------
+NORM_NONE, NORM_WHOLE, NORM_PER_HEAD = 0, 1, 2
+VMIX_NONE, VMIX_PUBLISH, VMIX_BLEND = 0, 1, 2
+
+
+def qkv_prep(y, offs, meta, q_out, kcache, vcache, H, G, dim, vdim, eps, bias=None, wconv=None, conv_state=None, taps=1, norm_mode=NORM_NONE,
+             qnorm_w=None, knorm_w=None, temp_coef=0.0, temp_every=0, freq=None, rot_dims=0, rot_halves=False, rot_mag=1.0, vmix_mode=VMIX_NONE,
+             vmix=0.0, v_first=None):
+    """The q | k | v columns of ``y`` (column offsets ``offs``) become attention inputs (csrc/window_attn.cu, qkv_prep): bias,
+    short causal convolution, RMS norm of q and k, query temperature, rotation of channel pairs, value blend; q into ``q_out``
+    (fp32), k and v into the caches at every row's (slot, position)."""
+    ld = _rowmajor(y, "y")
+    _req(meta, "meta", I32); _req(q_out, "q_out", F32)
+    M, C = y.shape[0], (H + G) * dim + G * vdim
+    for t, n, shape in ((bias, "bias", (C,)), (wconv, "wconv", (C, taps)), (v_first, "v_first", (M, G * vdim))):
+        if t is not None and tuple(_req(t, n, F32).shape) != shape:
+            raise _lib.LiaError(f"qkv_prep: {n} must be fp32 {shape}, got {tuple(t.shape)}")
+    if taps > 1 and (conv_state is None or tuple(_req(conv_state, "conv_state", F32).shape[1:]) != (taps - 1, C)):
+        raise _lib.LiaError("qkv_prep: the convolution's state must be fp32 [slots, taps - 1, channels]")
+    nw = {NORM_NONE: (0, 0), NORM_WHOLE: (H * dim, G * dim), NORM_PER_HEAD: (dim, dim)}[norm_mode]
+    if norm_mode != NORM_NONE and (_req(qnorm_w, "qnorm_w", F32).numel(), _req(knorm_w, "knorm_w", F32).numel()) != nw:
+        raise _lib.LiaError(f"qkv_prep: norm weights must have {nw} numbers")
+    if rot_dims and (freq is None or freq.dtype != torch.float64 or not freq.is_cuda or freq.numel() != rot_dims // 2):
+        raise _lib.LiaError("qkv_prep: the rotation needs rot_dims / 2 frequencies as a CUDA float64 tensor")
+    if not (kcache.dtype == vcache.dtype == y.dtype and kcache.is_contiguous() and vcache.is_contiguous() and kcache.shape[2] == G * dim
+            and vcache.shape[2] == G * vdim and tuple(q_out.shape) == (M, H * dim)):
+        raise _lib.LiaError("qkv_prep: caches must be contiguous [slots, capacity, G * dim | G * vdim] tensors of the activations' dtype, q_out [M, H * dim]")
+    check(_lib.load().lia_qkv_prep(_p(y), _f32(y), ld, offs[0], offs[1], offs[2], _p(bias), _p(wconv), _p(conv_state) if taps > 1 else None, int(taps),
+                                   norm_mode, _p(qnorm_w), _p(knorm_w), float(eps), float(temp_coef), int(temp_every), _p(freq), int(rot_dims),
+                                   int(rot_halves), float(rot_mag), vmix_mode, float(vmix), _p(v_first), _p(meta), _p(q_out), _p(kcache),
+                                   kcache.stride(0), _p(vcache), vcache.stride(0), M, H, G, dim, vdim, _stream()), "lia_qkv_prep")
+    count_launches()
+
+
+def gated_rms_add(x, y, w, h, eps, gate=None, gate_bias=None, stack=None, n_mix=0, mix=None):
+    """x += w * g / rms(g) with g = y * sigmoid(gate + gate_bias) (``gate``: a column slice of the activations' dtype; None: g = y;
+    ``y`` None: nothing is added).  With ``stack`` [n, rows, W] fp32: stack[n_mix - 1] = x and x = sum_j mix[j] * stack[j], j < n_mix.
+    ``h`` (may be None) receives x in the activations' dtype.  x is the fp32 residual stream, updated in place."""
+    _req(x, "x", F32)
+    rows, W = x.shape
+    for t, n in ((y, "y"), (h, "h")):
+        if t is not None and not (t.is_cuda and t.is_contiguous() and tuple(t.shape) == (rows, W)):
+            raise _lib.LiaError(f"gated_rms_add: {n} must be a contiguous CUDA [{rows}, {W}] tensor")
+    ldr = 0
+    if gate is not None:
+        ldr = _rowmajor(gate, "gate")
+        if h is None or gate.dtype != h.dtype or tuple(gate.shape) != (rows, W):
+            raise _lib.LiaError("gated_rms_add: the gate must be a [rows, W] slice of h's dtype")
+    for t, n in ((w, "w"), (gate_bias, "gate_bias")):
+        if t is not None and _req(t, n, F32).numel() != W:
+            raise _lib.LiaError(f"gated_rms_add: {n} must be fp32 [{W}]")
+    if stack is not None:
+        _req(stack, "stack", F32); _req(mix, "mix", F32)
+        if tuple(stack.shape[1:]) != (rows, W) or not 1 <= n_mix <= stack.shape[0] or mix.numel() < n_mix:
+            raise _lib.LiaError("gated_rms_add: stack must be [n, rows, W] with n >= n_mix, mix at least n_mix numbers")
+    act = h if h is not None else gate
+    check(_lib.load().lia_gated_rms_add(_p(x), _p(y), _f32(y) if y is not None else 0, _p(gate), ldr, _p(gate_bias), _p(w), _p(stack),
+                                        stack.stride(0) if stack is not None else 0, int(n_mix), _p(mix), _p(h), _f32(act) if act is not None else 1,
+                                        rows, W, float(eps), _stream()), "lia_gated_rms_add")
+    count_launches()
+    return x
+
+
+def poly_norm(inp, F, coef, out, eps):
+    """out = a N(z) + b N(z^2) + c N(z^3) + e over z = inp[:, :F], N = division by the row's root mean square; coef fp32 [4]."""
+    ld = _rowmajor(inp, "inp")
+    M = inp.shape[0]
+    if tuple(out.shape) != (M, F) or not out.is_contiguous() or out.dtype != inp.dtype or _req(coef, "coef", F32).numel() != 4:
+        raise _lib.LiaError("poly_norm: out must be a contiguous [M, F] tensor of the input's dtype, coef fp32 [4]")
+    check(_lib.load().lia_poly_norm(_p(inp), ld, _p(coef), _p(out), _f32(out), M, F, float(eps), _stream()), "lia_poly_norm")
+    count_launches()
     return out

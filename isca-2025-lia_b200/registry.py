@@ -27,12 +27,19 @@ def _bebulorn():
     return BebulornForCausalLM
 
 
+def _bizetar():
+    from .modeling_bizetar import BizetarForCausalLM
+    return BizetarForCausalLM
+
+
 register("OPTForCausalLM", _opt)
 register("opt", _opt)
 register("Davasun", _davasun)
 register("DavasunForCausalLM", _davasun)
 register("Bebulorn", _bebulorn)
 register("BebulornForCausalLM", _bebulorn)
+register("Bizetar", _bizetar)
+register("BizetarForCausalLM", _bizetar)
 
 
 def architecture_of(path):

@@ -1,8 +1,11 @@
 """Sequence mixers and feed-forwards that run on a 32-bit residual stream, each with its constants as parameters so that
 any model design can assemble them: a matrix-memory recurrent mixer (mLSTM), attention over a latent key/value cache with
 a partly rotated query/key and an output gate, linear attention with a fixed decay per head, the gated delta rule behind a
-short convolution, sliding-window attention with grouped key/value heads, and the feed-forwards -- clamped gated, plain
-gated with any activation, and a routed mixture of experts with a shared expert.  Each object owns its (fused) weights,
+short convolution, sliding-window attention with grouped key/value heads, attention over the whole history with a sink in the
+softmax (behind an optional bias, convolution, norm, temperature and rotation of its inputs, with a distance bias, a blend of
+values across layers and an output gate), and the feed-forwards -- clamped gated, plain gated with any activation, one with a
+polynomial activation between norms, and a routed mixture of experts (plain or gated experts, a shared expert, experts that
+hand the token back).  Each object owns its (fused) weights,
 registers its per-sequence state with a ``seq_state.SlotState`` and runs one step over a batch of portions
 (``StepBatch``) through the kernels of ``ops``.
 
@@ -29,6 +32,7 @@ class StepBatch:
     def __init__(self, rows, segs, meta, max_ctx=0):
         self.rows, self.segs, self.meta = rows, segs, meta
         self.max_ctx = max_ctx              # longest history (tokens cached after this step) among the step's sequences
+        self.scratch = {}                   # what one layer of this step leaves for later layers (per-token tensors)
 
 
 class Linear:
@@ -277,6 +281,142 @@ class WindowAttentionMixer:
         return self.out(o)
 
 
+def scaled_rotary_freq(dims, base, scaling=None):
+    """Rotation frequencies f_i = base^(-2i/dims), i < dims/2, as float64, and the factor on cos and sin.  With ``scaling``
+    {factor, original, fast, slow} (the "YaRN" interpolation): pairs that turn more than ``fast`` times within ``original``
+    positions keep f_i, those that turn fewer than ``slow`` times get f_i / factor, the ones between are blended linearly in
+    the pair index, and cos and sin are multiplied by 0.1 ln(factor) + 1."""
+    import math
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = float(base) ** (-2.0 * i / dims)
+    if not scaling:
+        return f, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def pair_at(turns):                     # the (real-valued) pair index whose frequency makes `turns` turns in `original` positions
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+
+    lo = max(math.floor(pair_at(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(pair_at(float(scaling["slow"]))), dims - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+class SinkAttentionMixer:
+    """Causal softmax attention over the whole history with grouped key/value heads and one learned sink per head in the
+    softmax's denominator (a term without key or value).  Everything else is an option, so that designs which differ in them
+    share the mixer:
+      ``biases``   q, k, v projections with biases ("q.b", ...);
+      ``taps``     > 1: a short causal convolution over time on every channel of q, k, v right after the projection
+                   ("q.conv" [channels, taps], ...); the last taps - 1 projected rows are per-sequence state;
+      ``norm``     "whole": one RMS norm over all of q and one over all of k ("q.norm" [H*dim], "k.norm" [G*dim]);
+                   "head": per head with a weight [dim] shared by the heads;
+      ``q_temp``   (coef, every): q times 1 + coef * ln(floor((pos + 1) / every) + 1);
+      ``rot``      {"dims", "base", "scaling"}: the first ``dims`` channels of every q and k head turn in pairs (2i, 2i+1);
+      ``slopes``   [H]: slope_h * (i - j) is taken off the score of query i and key j;
+      ``v_mix``    "publish": this layer's values are left in the step's scratch for later layers; "blend": v becomes
+                   (1 - vmix) v + vmix v_published before it is cached;
+      ``gate``     "head": head h's output times sigmoid(Wg h)_h; "channel": the concatenated heads times sigmoid(Wg h);
+      ``ride_along`` further weight matrices that read the same input: they join the stacked projection and their outputs
+                   (column slices) are appended to ``extras`` by ``__call__``.
+    Norms, temperature, angles, scores, weights and sums are fp32; q stays fp32 up to the scores; the caches hold the
+    model's dtype (csrc/window_attn.cu)."""
+
+    def __init__(self, w, heads, kv_heads, dim, vdim, scale, norm_eps, dtype, device, norm=None, biases=False, taps=1, q_temp=None, rot=None,
+                 slopes=None, v_mix=None, gate=None, ride_along=()):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} heads do not divide into {kv_heads} key/value heads")
+        if norm not in (None, "whole", "head") or gate not in (None, "head", "channel") or v_mix not in (None, "publish", "blend"):
+            raise ValueError(f"unknown option: norm={norm!r} gate={gate!r} v_mix={v_mix!r}")
+        self.H, self.G, self.dim, self.vdim, self.taps = heads, kv_heads, dim, vdim, int(taps)
+        self.scale, self.eps, self.dtype = float(scale), float(norm_eps), dtype
+        nq, nk, nv = heads * dim, kv_heads * dim, kv_heads * vdim
+        self.channels = nq + nk + nv
+        stacked = [w["q"], w["k"], w["v"]] + ([w["g"]] if gate == "channel" else []) + list(ride_along)
+        self.n_ride, self.gate = len(ride_along), gate
+        self.proj = Linear(stacked, dtype, device)
+        f32 = dict(device=device, dtype=F32)
+        self.bias = torch.cat([w["q.b"], w["k.b"], w["v.b"]]).to(**f32).contiguous() if biases else None
+        self.w_conv = torch.cat([w["q.conv"], w["k.conv"], w["v.conv"]], 0).to(**f32).contiguous() if self.taps > 1 else None
+        self.norm_mode = {None: ops.NORM_NONE, "whole": ops.NORM_WHOLE, "head": ops.NORM_PER_HEAD}[norm]
+        self.q_norm = w["q.norm"].to(**f32).contiguous() if norm else None
+        self.k_norm = w["k.norm"].to(**f32).contiguous() if norm else None
+        self.temp_coef, self.temp_every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
+        self.rot_dims, self.freq, self.rot_mag = 0, None, 1.0
+        if rot:
+            self.rot_dims = int(rot["dims"])
+            if self.rot_dims % 2 or not 0 < self.rot_dims <= dim:
+                raise ValueError(f"cannot rotate {self.rot_dims} of {dim} channels")
+            f, self.rot_mag = scaled_rotary_freq(self.rot_dims, rot["base"], rot.get("scaling"))
+            self.freq = f.to(device).contiguous()
+        self.slopes = torch.tensor([float(x) for x in slopes], dtype=torch.float64).to(**f32) if slopes is not None else None
+        self.sink = w["sink"].to(**f32).contiguous()
+        self.vmix_mode = {None: ops.VMIX_NONE, "publish": ops.VMIX_PUBLISH, "blend": ops.VMIX_BLEND}[v_mix]
+        self.vmix = float(w["vmix"]) if v_mix == "blend" else 0.0
+        self.w_gate = w["g"].to(device=device, dtype=dtype).contiguous() if gate == "head" else None
+        self.out = Linear([w["o"]], dtype, device)
+
+    def new_state(self, slots):
+        st = (slots.add_rows(self.G * self.dim, self.dtype), slots.add_rows(self.G * self.vdim, self.dtype))
+        if self.taps > 1:
+            st += (slots.add_recurrent((self.taps - 1, self.channels)),)
+        return st
+
+    def __call__(self, h, batch, state, extras=None):
+        kc, vc = state[0], state[1]
+        conv = state[2] if self.taps > 1 else None
+        M, H, G = h.shape[0], self.H, self.G
+        y = self.proj(h)
+        first_ride = 3 + (self.gate == "channel")
+        if extras is not None:
+            extras.extend(self.proj.part(y, first_ride + i) for i in range(self.n_ride))
+        gate = None
+        if self.gate == "head":
+            gate = torch.empty(M, H, dtype=F32, device=h.device)
+            ops.linear_small(h, self.w_gate, None, gate, ops.GATE_SIGMOID)
+        elif self.gate == "channel":
+            gate = self.proj.part(y, 3)
+        v_first = None
+        if self.vmix_mode == ops.VMIX_PUBLISH:
+            v_first = batch.scratch["v_first"] = torch.empty(M, G * self.vdim, dtype=F32, device=h.device)
+        elif self.vmix_mode == ops.VMIX_BLEND:
+            v_first = batch.scratch["v_first"]
+            if v_first.shape[1] != G * self.vdim:
+                raise ValueError(f"values of {G * self.vdim} numbers cannot be blended with published values of {v_first.shape[1]}")
+        q = torch.empty(M, H * self.dim, dtype=F32, device=h.device)
+        offs = self.proj.offsets[:3]
+        ops.qkv_prep(y, offs, batch.meta, q, kc, vc, H, G, self.dim, self.vdim, self.eps, bias=self.bias, wconv=self.w_conv, conv_state=conv,
+                     taps=self.taps, norm_mode=self.norm_mode, qnorm_w=self.q_norm, knorm_w=self.k_norm, temp_coef=self.temp_coef,
+                     temp_every=self.temp_every, freq=self.freq, rot_dims=self.rot_dims, rot_mag=self.rot_mag, vmix_mode=self.vmix_mode,
+                     vmix=self.vmix, v_first=v_first)
+        if self.taps > 1:
+            ops.conv_state_update(y, offs, H * self.dim, G * self.vdim, conv, batch.segs, self.taps, nk=G * self.dim)
+        o = torch.empty(M, H * self.vdim, dtype=self.dtype, device=h.device)
+        ops.window_attn(q, kc, vc, batch.meta, None, o, H, G, self.dim, self.vdim, 0, self.scale, 0.0, nseg=batch.segs.shape[0],
+                        max_ctx=batch.max_ctx, slopes=self.slopes, sink=self.sink, gate=gate, gate_per_head=self.gate == "head")
+        return self.out(o)
+
+
+class PolyNormMLP:
+    """Wdown act(Wup h) with the polynomial activation between norms: act(z) = a N(z) + b N(z^2) + c N(z^3) + e, powers taken
+    element by element, N = division of a token's ff numbers by their root mean square (fp32).  ``ride_along``: further weight
+    matrices that read the same input and join the up projection (outputs appended to ``extras``)."""
+
+    def __init__(self, w, ff, norm_eps, dtype, device, ride_along=()):
+        self.ff, self.eps, self.dtype, self.n_ride = ff, float(norm_eps), dtype, len(ride_along)
+        self.up = Linear([w["up"]] + list(ride_along), dtype, device)
+        self.coef = w["act"].to(device=device, dtype=F32).contiguous()
+        self.down = Linear([w["down"]], dtype, device)
+
+    def __call__(self, h, extras=None):
+        u = self.up(h)
+        if extras is not None:
+            extras.extend(self.up.part(u, 1 + i) for i in range(self.n_ride))
+        y = torch.empty(h.shape[0], self.ff, dtype=self.dtype, device=h.device)
+        ops.poly_norm(u, self.ff, self.coef, y, self.eps)
+        return self.down(y)
+
+
 class GatedMLP:
     """Dense gated feed-forward: Wdown (act(Wgate h) * (Wup h))."""
 
@@ -308,21 +448,28 @@ class PlainMLP:
 
 
 class MoEFeedForward:
-    """Routed mixture of experts: router logits in fp32, softmax over all experts, the ``top`` largest scores renormalised
-    (divided by their sum + 1e-20); every expert is Wdown act(Wup h); a shared expert (optional) runs for every token and is
-    added.  ``experts_w``: list of {"up", "down"} per expert.  The (token, choice) pairs are grouped by expert on the device
-    (no host round trip) and each projection runs as one grouped launch; a handful of pairs (decoding) take the form with one
-    warp per output instead.  The result is fp32."""
+    """Routed mixture of experts: router logits in fp32, softmax over all experts, the ``top`` largest scores (``correction``,
+    one number per router output, is added for the choice only) as weights, renormalised (divided by their sum + 1e-20) if
+    ``renorm``; every expert is Wdown act(Wup h), or Wdown (act(Wgate h) * Wup h) when ``experts_w`` carry a "gate"; the last
+    ``identity`` router outputs are experts without weights that hand the token back; a shared expert (optional) runs for
+    every token and is added.  ``experts_w``: list of {"up", "down"[, "gate"]} per expert.  The (token, choice) pairs are
+    grouped by expert on the device (no host round trip) and each projection runs as one grouped launch; a handful of pairs
+    (decoding) take the form with one warp per output instead.  The result is fp32."""
 
     FEW_PAIRS = 48            # up to here: one warp per output, no plan
     TENSOR_CORE_PAIRS = 512   # from here (bf16, sizes that are multiples of 8): every expert's rows through the tensor-core GEMM
 
-    def __init__(self, router_w, experts_w, top, ff, act, shared, dtype, device):
+    def __init__(self, router_w, experts_w, top, ff, act, shared, dtype, device, correction=None, renorm=True, identity=0):
         self.E, self.top, self.ff, self.act, self.dtype = len(experts_w), int(top), ff, act, dtype
-        if not 1 <= self.top <= self.E:
-            raise ValueError(f"top = {top} of {self.E} experts")
+        self.identity, self.renorm = int(identity), bool(renorm)
+        self.R = self.E + self.identity                          # router outputs
+        if not 1 <= self.top <= self.R or self.E < 1 or router_w.shape[0] != self.R:
+            raise ValueError(f"top = {top} of {self.E} experts + {self.identity} identity experts, router of {router_w.shape[0]} outputs")
         self.router = router_w.to(device=device, dtype=dtype).contiguous()
-        self.w_up = torch.stack([e["up"] for e in experts_w]).to(device=device, dtype=dtype).contiguous()         # [E, ff, W]
+        self.correction = correction.to(device=device, dtype=F32).contiguous() if correction is not None else None
+        self.gated = "gate" in experts_w[0]
+        # [E, ff, W], or [E, 2 ff, W] with every expert's gate rows before its up rows
+        self.w_up = torch.stack([torch.cat([e["gate"], e["up"]], 0) if self.gated else e["up"] for e in experts_w]).to(device=device, dtype=dtype).contiguous()
         self.w_down = torch.stack([e["down"] for e in experts_w]).to(device=device, dtype=dtype).contiguous()     # [E, W, ff]
         self.shared = shared
         W = self.w_up.shape[2]
@@ -342,34 +489,38 @@ class MoEFeedForward:
         GEMM per expert and projection on its contiguous rows (launched back to back from the library).  The tile table comes to the host once per call (the only
         round trip; decode steps never take this path, so they stay capturable)."""
         M, W = h.shape
-        E, top, ff, dev = self.E, self.top, self.ff, h.device
+        E, R, top, ff, dev = self.E, self.R, self.top, self.ff, h.device
         pairs = M * top
-        n_tiles, tm = ops.moe_tiles(pairs, E)
+        n_tiles, tm = ops.moe_tiles(pairs, R)
         perm = torch.empty(n_tiles * tm, dtype=torch.int32, device=dev)
         tile_expert = torch.empty(n_tiles, dtype=torch.int32, device=dev)
         pos_of = torch.empty(pairs, dtype=torch.int32, device=dev)
-        ops.moe_plan(idx, E, perm, tile_expert, pos_of)
+        ops.moe_plan(idx, R, perm, tile_expert, pos_of)
         xs = torch.empty(n_tiles * tm, W, dtype=self.dtype, device=dev)
         ops.moe_gather(h, perm, xs, top)
-        counts = torch.bincount(tile_expert.cpu().long() + 1, minlength=E + 1)[1:].tolist()          # tiles per expert
-        used, rows = sum(counts) * tm, [n * tm for n in counts if n]
-        up = torch.empty(used, ff, dtype=self.dtype, device=dev)
-        ops.moe_expert_gemms(xs, self.w_up, up, counts, tm, self._workspace(rows, ff, W, dev))
+        counts = torch.bincount(tile_expert.cpu().long() + 1, minlength=R + 1)[1:E + 1].tolist()     # tiles per expert that has weights (they come first)
+        used, rows = max(sum(counts), 1) * tm, [n * tm for n in counts if n]
+        n_up = self.w_up.shape[1]
+        up = torch.empty(used, n_up, dtype=self.dtype, device=dev)
         mid = torch.empty(used, ff, dtype=self.dtype, device=dev)
-        ops.gated_act(up, ff, mid, self.act)
         ys = torch.empty(used, W, dtype=self.dtype, device=dev)
-        ops.moe_expert_gemms(mid, self.w_down, ys, counts, tm, self._workspace(rows, W, ff, dev))
-        ops.moe_combine(ys, self.shared(h) if self.shared is not None else None, y, top, pos_of=pos_of, wt=wt)
+        if rows:
+            ops.moe_expert_gemms(xs, self.w_up, up, counts, tm, self._workspace(rows, n_up, W, dev))
+            ops.gated_act(up, ff, mid, self.act, up_off=ff if self.gated else -1)
+            ops.moe_expert_gemms(mid, self.w_down, ys, counts, tm, self._workspace(rows, W, ff, dev))
+        ops.moe_combine(ys, self.shared(h) if self.shared is not None else None, y, top, pos_of=pos_of, wt=wt,
+                        identity=(idx, E, h, wt) if self.identity else None)
         return y
 
     def __call__(self, h):
         M, W, dev = h.shape[0], h.shape[1], h.device
-        E, top = self.E, self.top
-        logits = torch.empty(M, E, dtype=F32, device=dev)
+        R, top = self.R, self.top
+        logits = torch.empty(M, R, dtype=F32, device=dev)
         ops.linear_small(h, self.router, None, logits, ops.GATE_NONE)
         idx = torch.empty(M, top, dtype=torch.int32, device=dev)
         wt = torch.empty(M, top, dtype=F32, device=dev)
-        ops.router_topk(logits, top, idx, wt)
+        ops.router_topk(logits, top, idx, wt, correction=self.correction, renorm=self.renorm)
+        identity = (idx, self.E, h, wt) if self.identity else None
         pairs = M * top
         y = torch.empty(M, W, dtype=F32, device=dev)
         if self.tensor_core and pairs >= self.TENSOR_CORE_PAIRS and h.is_contiguous() and not torch.cuda.is_current_stream_capturing():
@@ -377,16 +528,16 @@ class MoEFeedForward:
         ypair = torch.empty(pairs, W, dtype=F32, device=dev)
         if pairs <= self.FEW_PAIRS:
             mid = torch.empty(pairs, self.ff, dtype=self.dtype, device=dev)
-            ops.moe_gemm(h, self.w_up, mid, idx, wt, top, True, self.act)
+            ops.moe_gemm(h, self.w_up, mid, idx, wt, top, True, self.act, gated=self.gated)
             ops.moe_gemm(mid, self.w_down, ypair, idx, wt, top, False)
         else:
-            n_tiles, tm = ops.moe_tiles(pairs, E)
+            n_tiles, tm = ops.moe_tiles(pairs, R)
             perm = torch.empty(n_tiles * tm, dtype=torch.int32, device=dev)
             tile_expert = torch.empty(n_tiles, dtype=torch.int32, device=dev)
             pos_of = torch.empty(pairs, dtype=torch.int32, device=dev)
-            ops.moe_plan(idx, E, perm, tile_expert, pos_of)
+            ops.moe_plan(idx, R, perm, tile_expert, pos_of)
             mid = torch.empty(n_tiles * tm, self.ff, dtype=self.dtype, device=dev)
-            ops.moe_gemm(h, self.w_up, mid, idx, wt, top, True, self.act, perm, tile_expert)
+            ops.moe_gemm(h, self.w_up, mid, idx, wt, top, True, self.act, perm, tile_expert, gated=self.gated)
             ops.moe_gemm(mid, self.w_down, ypair, idx, wt, top, False, ops.ACT_NONE, perm, tile_expert)
-        ops.moe_combine(ypair, self.shared(h) if self.shared is not None else None, y, top)
+        ops.moe_combine(ypair, self.shared(h) if self.shared is not None else None, y, top, identity=identity)
         return y
