@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(128) kv_store_kernel(const T* __restrict__ k, 
 struct PrepArgs {
   int H, G, dim, vdim;
   int q_off, k_off, v_off;       // columns of q | k | v in a row of the projection's output
-  int taps;                      // 1: no convolution
+  int taps;                      // of the convolution, if it has weights
   int norm_mode;                 // 0 none; 1 one RMS norm over all of q (and all of k), weights [H*dim], [G*dim]; 2 per head, weights [dim]
   int temp_every;                // > 0: q *= 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)
   int rot_dims, rot_halves;      // channels (2i, 2i+1), i < rot_dims/2, of every head turn by pos * freq[i]; rot_halves != 0: pairs (i, i + rot_dims/2)
@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(256) qkv_prep_kernel(const T* __restrict__ y, 
     const int col = c < nq ? a.q_off + c : (c < nq + nk ? a.k_off + (c - nq) : a.v_off + (c - nq - nk));
     const float b = bias ? bias[c] : 0.f;
     float acc;
-    if (a.taps > 1) {
+    if (wconv != nullptr) {
       acc = 0.f;
       for (int j = 0; j < a.taps && j <= pos; ++j) {          // j tokens back
         const float xin = j < inside ? ldf(y + (size_t)(row - j) * ld + col) : st[(size_t)(inside - 1 - j + a.taps - 1) * C + c];

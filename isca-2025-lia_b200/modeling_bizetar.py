@@ -103,8 +103,8 @@ class BizetarConfig:
             else:
                 out.update({p + "mix.q.norm": (d,), p + "mix.k.norm": (d,), p + "mix.g": (H * v, W),
                             p + "mix.q.b": (H * d,), p + "mix.k.b": (G * d,), p + "mix.v.b": (G * v,)})
-                taps = m.get("conv") or 1
-                if taps > 1:
+                taps = m.get("conv")
+                if taps:
                     out.update({p + "mix.q.conv": (H * d, taps), p + "mix.k.conv": (G * d, taps), p + "mix.v.conv": (G * v, taps)})
             mlp = l.get("mlp")
             if mlp is None:
@@ -177,7 +177,7 @@ class BizetarForCausalLM:
                                            q_temp=(qt["coef"], qt["every"]) if qt else None, slopes=distance_slopes(m["heads"]), gate="head", **common)
             else:
                 mixer = SinkAttentionMixer(w, m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["scale"], norm="head", biases=True,
-                                           taps=m.get("conv") or 1, rot=m.get("rot"), gate="channel", **common)
+                                           taps=m.get("conv"), rot=m.get("rot"), gate="channel", **common)
             mlp = norm2 = rg2 = rg2_b = None
             spec = l.get("mlp")
             if spec is not None:

@@ -780,7 +780,7 @@ def qkv_prep(y, offs, meta, q_out, kcache, vcache, H, G, dim, vdim, eps, bias=No
     if not (kcache.dtype == vcache.dtype == y.dtype and kcache.is_contiguous() and vcache.is_contiguous() and kcache.shape[2] == G * dim
             and vcache.shape[2] == G * vdim and tuple(q_out.shape) == (M, H * dim)):
         raise _lib.LiaError("qkv_prep: caches must be contiguous [slots, capacity, G * dim | G * vdim] tensors of the activations' dtype, q_out [M, H * dim]")
-    check(_lib.load().lia_qkv_prep(_p(y), _f32(y), ld, offs[0], offs[1], offs[2], _p(bias), _p(wconv), _p(conv_state) if taps > 1 else None, int(taps),
+    check(_lib.load().lia_qkv_prep(_p(y), _f32(y), ld, offs[0], offs[1], offs[2], _p(bias), _p(wconv), _p(conv_state) if taps > 1 else None, int(taps) if wconv is not None else 1,
                                    norm_mode, _p(qnorm_w), _p(knorm_w), float(eps), float(temp_coef), int(temp_every), _p(freq), int(rot_dims),
                                    int(rot_halves), float(rot_mag), vmix_mode, float(vmix), _p(v_first), _p(meta), _p(q_out), _p(kcache),
                                    kcache.stride(0), _p(vcache), vcache.stride(0), M, H, G, dim, vdim, _stream()), "lia_qkv_prep")

@@ -307,8 +307,8 @@ class SinkAttentionMixer:
     softmax's denominator (a term without key or value).  Everything else is an option, so that designs which differ in them
     share the mixer:
       ``biases``   q, k, v projections with biases ("q.b", ...);
-      ``taps``     > 1: a short causal convolution over time on every channel of q, k, v right after the projection
-                   ("q.conv" [channels, taps], ...); the last taps - 1 projected rows are per-sequence state;
+      ``taps``     a short causal convolution over time on every channel of q, k, v right after the projection ("q.conv"
+                   [channels, taps], ...; None: no convolution); the last taps - 1 projected rows are per-sequence state;
       ``norm``     "whole": one RMS norm over all of q and one over all of k ("q.norm" [H*dim], "k.norm" [G*dim]);
                    "head": per head with a weight [dim] shared by the heads;
       ``q_temp``   (coef, every): q times 1 + coef * ln(floor((pos + 1) / every) + 1);
@@ -322,13 +322,13 @@ class SinkAttentionMixer:
     Norms, temperature, angles, scores, weights and sums are fp32; q stays fp32 up to the scores; the caches hold the
     model's dtype (csrc/window_attn.cu)."""
 
-    def __init__(self, w, heads, kv_heads, dim, vdim, scale, norm_eps, dtype, device, norm=None, biases=False, taps=1, q_temp=None, rot=None,
+    def __init__(self, w, heads, kv_heads, dim, vdim, scale, norm_eps, dtype, device, norm=None, biases=False, taps=None, q_temp=None, rot=None,
                  slopes=None, v_mix=None, gate=None, ride_along=()):
         if heads % kv_heads:
             raise ValueError(f"{heads} heads do not divide into {kv_heads} key/value heads")
         if norm not in (None, "whole", "head") or gate not in (None, "head", "channel") or v_mix not in (None, "publish", "blend"):
             raise ValueError(f"unknown option: norm={norm!r} gate={gate!r} v_mix={v_mix!r}")
-        self.H, self.G, self.dim, self.vdim, self.taps = heads, kv_heads, dim, vdim, int(taps)
+        self.H, self.G, self.dim, self.vdim, self.taps = heads, kv_heads, dim, vdim, int(taps or 1)
         self.scale, self.eps, self.dtype = float(scale), float(norm_eps), dtype
         nq, nk, nv = heads * dim, kv_heads * dim, kv_heads * vdim
         self.channels = nq + nk + nv
@@ -337,7 +337,7 @@ class SinkAttentionMixer:
         self.proj = Linear(stacked, dtype, device)
         f32 = dict(device=device, dtype=F32)
         self.bias = torch.cat([w["q.b"], w["k.b"], w["v.b"]]).to(**f32).contiguous() if biases else None
-        self.w_conv = torch.cat([w["q.conv"], w["k.conv"], w["v.conv"]], 0).to(**f32).contiguous() if self.taps > 1 else None
+        self.w_conv = torch.cat([w["q.conv"], w["k.conv"], w["v.conv"]], 0).to(**f32).contiguous() if taps else None
         self.norm_mode = {None: ops.NORM_NONE, "whole": ops.NORM_WHOLE, "head": ops.NORM_PER_HEAD}[norm]
         self.q_norm = w["q.norm"].to(**f32).contiguous() if norm else None
         self.k_norm = w["k.norm"].to(**f32).contiguous() if norm else None

@@ -51,7 +51,7 @@ CASES = {
                    attention_2(3, 3, 12, 34, conv=5, rot_dims=None, mlp=moe(5, 3, 11, identity=3)), attention(5, 5, 6, 3, q_temp=None)],
                   vocab=61, width=44, eps=1e-6),
     # wide heads (dim > 64, vdim > 64), nine query heads on three key/value heads, value mixing from the first layer, a
-    # rotation that covers part of a head with frequencies that are all interpolated
+    # rotation that covers part of a head with all frequencies but the first interpolated
     "wide": config([attention(9, 3, 72, 40, v_mix=True), attention_2(3, 3, 80, 40, conv=2, rot_dims=34, base=50.0, scaling=(16.0, 32, 1000.0, 500.0), v_mix=True, mlp=dense(16)),
                     attention_2(2, 1, 136, 120, conv=3, rot_dims=136, v_mix=True)], vocab=90, width=96),
 }
