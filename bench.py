@@ -64,6 +64,8 @@ def parse():
                          "Davasun beside OPT at equal width and depth (1 GPU, random weights); prints one JSON object")
     ap.add_argument("--compare-bebulorn", action="store_true",
                     help="instead of the headline workload: the same comparison for Bebulorn beside Davasun, its closest existing model")
+    ap.add_argument("--compare-bizetar", action="store_true",
+                    help="instead of the headline workload: the same comparison for Bizetar beside Bebulorn, its closest existing model")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
@@ -405,6 +407,11 @@ def _main(args, json_out):
         from lia_b200 import bench_compare
         if rank == 0:
             json_out.write(json.dumps(bench_compare.run_bebulorn(peaks())) + "\n")
+        return 0
+    if args.compare_bizetar:
+        from lia_b200 import bench_compare
+        if rank == 0:
+            json_out.write(json.dumps(bench_compare.run_bizetar(peaks())) + "\n")
         return 0
     from lia_b200.modeling_opt import get_config
     cfg = get_config(args.model)

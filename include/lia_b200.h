@@ -358,7 +358,7 @@ int lia_moe_combine(const void* ypair, int ypair_f32, const int* pos_of, const f
 int lia_moe_combine_ext(const void* ypair, int ypair_f32, const int* pos_of, const float* wt, const void* shared, int act_f32, const int* idx,
                         int n_real, const void* h, float* y, int M, int W, int top, lia_stream_t stream);
 
-/* Short causal convolution (taps <= 8, weights [channels][taps], last column = current token) + SiLU over the q | k | v
+/* Short causal convolution (taps <= 16, weights [channels][taps], last column = current token) + SiLU over the q | k | v
  * channels of a projection's output y (row stride ld, column offsets given; q and k have G heads of dim, v has H of vdim);
  * q and k divided by sqrt(sum of squares + unit_eps) per head, q times q_scale; gates [M][2H] hold W_b h | W_a h on entry and
  * beta = sigmoid(.) | g = exp(-exp(a_log) * softplus(. + dt_bias)) on return.  conv_state [slot][taps-1][channels] fp32 holds
@@ -405,7 +405,7 @@ int lia_window_attn_ext(const void* q, int ldq, int q_f32, int act_f32, const vo
 /* What turns the q | k | v columns of a projection's output y (row stride ld) into attention inputs, per token row with
  * meta[row] = {slot, position}; each step is optional and they come in this order:
  *   bias [H*dim + G*dim + G*vdim] added;
- *   a short causal convolution over time per channel (taps <= 8, wconv [channels][taps], last column = current token; the
+ *   a short causal convolution over time per channel (taps <= 16, wconv [channels][taps], last column = current token; the
  *   taps - 1 outputs of the projection before a portion come from conv_state [slot][taps-1][channels] fp32, kept current by
  *   lia_conv_state_update; what lies before the sequence's start is zero);
  *   RMS norm of q and of k -- norm_mode 1: over the whole projection, weights [H*dim] and [G*dim]; 2: per head, weights [dim];

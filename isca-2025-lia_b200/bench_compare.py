@@ -2,6 +2,8 @@
 beside OPT -- the closest existing model -- at equal width and depth, with every kernel's time against its roofline.
 `bench.py --compare-bebulorn`: the same for Bebulorn beside Davasun, the closest existing model (step-served, recurrent and
 attention mixers on a 32-bit residual stream).
+`bench.py --compare-bizetar`: the same for Bizetar beside Bebulorn, the closest existing model (softmax attention with grouped
+key/value heads on the same attention kernel, dense and mixture-of-experts feed-forwards, step-served).
 
 Each operation of ``ops`` is wrapped for the duration of an instrumented pass: CUDA events around the call, and the
 operation's algorithmic FLOPs and bytes from its arguments.  roofline time = max(FLOPs / peak, bytes / HBM bandwidth)
@@ -57,6 +59,19 @@ def _cost(name, a, kw):
         q, kc, out, H, G, dim, vdim = a[0], a[1], a[5], a[6], a[7], a[8], a[9]
         keys = float(kw.get("_wkeys", 0))                                          # sum over rows of keys inside the window
         return 2.0 * keys * H * (dim + vdim), _nbytes(q, out) + kw.get("_wctx", 0) * G * (dim + vdim) * kc.element_size(), "f32"
+    if name == "qkv_prep":
+        y, q_out, kc, vc = a[0], a[3], a[4], a[5]
+        M = y.shape[0]
+        C = q_out.shape[1] + kc.shape[2] + vc.shape[2]
+        return 0.0, M * (C * y.element_size() + q_out.shape[1] * 4 + (kc.shape[2] + vc.shape[2]) * kc.element_size()), "mem"
+    if name == "gated_rms_add":
+        x, y, h = a[0], a[1], a[3]
+        n_mix = kw.get("n_mix", 0) if kw.get("stack") is not None else 0
+        gate = kw.get("gate")
+        return 0.0, _nbytes(x) * (2 + n_mix) + _nbytes(y, h) + (x.shape[0] * x.shape[1] * gate.element_size() if gate is not None else 0), "mem"
+    if name == "poly_norm":
+        inp, F, out = a[0], a[1], a[3]
+        return 0.0, 2.0 * inp.shape[0] * F * inp.element_size() + _nbytes(out), "mem"
     if name == "moe_gemm":
         x, w, out, idx = a[0], a[1], a[2], a[3]
         pairs, N, K = idx.numel(), w.shape[1], w.shape[2]
@@ -83,7 +98,7 @@ class Instrument:
     NAMES = ("gemm", "linear_plain", "linear_small", "mlstm_scan", "headnorm_gate", "latent_prep", "latent_attn", "clamped_glu",
              "rms_add_norm", "embed_rmsnorm", "rms_gather", "layernorm", "attn_prefill", "attn_decode", "embed", "argmax", "argmax_f32",
              "linear_scan", "conv_prep", "conv_state_update", "kv_store", "window_attn", "ln_add_norm", "embed_rows", "ln_gather", "gated_act",
-             "router_topk", "moe_plan", "moe_gemm", "moe_gather", "moe_expert_gemms", "moe_combine")
+             "router_topk", "moe_plan", "moe_gemm", "moe_gather", "moe_expert_gemms", "moe_combine", "qkv_prep", "gated_rms_add", "poly_norm")
 
     def __init__(self):
         self.records, self.saved, self.extra = [], {}, {}
@@ -158,9 +173,26 @@ def bebulorn_config(width, n_layers):
             "loop": {"start": 0, "stop": 0, "times": 1}, "norm": {"eps": 1e-6}, "residual_mult": 0.5}
 
 
+def bizetar_config(width, n_layers):
+    """Layer sizes of a ~1-3 B model: heads of 128 x 128 on 8 key/value heads throughout; three layers in four rotate half of
+    every head behind a 4-tap convolution, the fourth norms the whole projection and takes a distance bias; every layer mixes
+    values; feed-forwards alternate between a dense 2.75 x one and 16 gated experts of 0.6875 x (2 chosen) with 2 identity experts."""
+    H = width // 128
+    G = min(8, H)
+    dense = {"kind": "dense", "ff": width * 11 // 4}
+    moe = {"kind": "moe", "router": {"experts": 16, "identity": 2, "top": 2}, "expert": {"ff": width * 11 // 16}}
+    base = {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "v_mix": True}
+    rot = {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}
+    a2 = lambda mlp: {"type": "attention_2", "mixer": dict(base, conv=4, rot=rot), "mlp": mlp}  # noqa: E731
+    a1 = {"type": "attention", "mixer": dict(base, q_temp={"coef": 0.1, "every": 256}), "mlp": moe}
+    pattern = [a2(dense), a1, a2(moe), a2(dense)]
+    return {"architecture": "Bizetar", "vocab": 32000, "width": width, "layers": [pattern[i % 4] for i in range(n_layers)], "norm": {"eps": 1e-6}}
+
+
 def _window_keys(layers, n_new, ctx_before):
-    """Sum over the new rows of the keys inside the first attention layer's window, and the cached rows those windows span."""
-    win = next((l["mixer"]["mask"]["size"] for l in layers if l["type"] == "attention"), 0)
+    """Sum over the new rows of the keys inside the first attention layer's window (the whole history where a layer names
+    none), and the cached rows those windows span."""
+    win = next((l["mixer"].get("mask", {}).get("size", 1 << 30) for l in layers if l["type"].startswith("attention")), 0)
     if not win:
         return 0, 0
     keys = sum(min(win, ctx_before + i + 1) for i in range(n_new))
@@ -217,6 +249,27 @@ def run_bebulorn(pk, widths=(2048, 4096), n_layers=8, prompt=2048, decode_ctx=20
         rec = {"width": width, "layers": n_layers, "prompt": prompt, "decode_context": decode_ctx}
         for name, make in (("bebulorn", lambda: BebulornForCausalLM(BebulornConfig.from_dict(bebulorn_config(width, n_layers)), dev, BF16)),
                            ("davasun", lambda: DavasunForCausalLM(DavasunConfig.from_dict(davasun_config(width, n_layers)), dev, BF16))):
+            m = make().init_weights(seed=1)
+            rec[name] = step_model(m, m.config, pk, g, prompt, decode_ctx, decode_batches, new)
+            del m
+            torch.cuda.empty_cache()
+        out["sizes"].append(rec)
+    return out
+
+
+def run_bizetar(pk, widths=(2048, 4096), n_layers=8, prompt=2048, decode_ctx=2048, decode_batches=(1, 16), new=16):
+    """Bizetar beside Bebulorn at equal width and depth."""
+    from .modeling_bebulorn import BebulornConfig, BebulornForCausalLM
+    from .modeling_bizetar import BizetarConfig, BizetarForCausalLM
+    dev = torch.device("cuda", 0)
+    props = torch.cuda.get_device_properties(dev)
+    pk = dict(pk, fp32_nominal_tflops=props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12)
+    out = {"peaks": pk, "sizes": []}
+    g = torch.Generator().manual_seed(0)
+    for width in widths:
+        rec = {"width": width, "layers": n_layers, "prompt": prompt, "decode_context": decode_ctx}
+        for name, make in (("bizetar", lambda: BizetarForCausalLM(BizetarConfig.from_dict(bizetar_config(width, n_layers)), dev, BF16)),
+                           ("bebulorn", lambda: BebulornForCausalLM(BebulornConfig.from_dict(bebulorn_config(width, n_layers)), dev, BF16))):
             m = make().init_weights(seed=1)
             rec[name] = step_model(m, m.config, pk, g, prompt, decode_ctx, decode_batches, new)
             del m

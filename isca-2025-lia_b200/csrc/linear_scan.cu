@@ -30,7 +30,7 @@ template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return _
 __device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }
 
 // ---------------------------------------------------------------------------------------------------- convolution + gates
-constexpr int MAX_TAPS = 8;
+constexpr int MAX_TAPS = 16;
 
 struct ConvCols {          // where the q, k, v channels sit in a row of the projection's output
   int q_off, k_off, v_off, nq, nk, nv;       // channels of q, of k and of v

@@ -532,7 +532,7 @@ extern "C" int lia_qkv_prep(const void* y, int act_f32, int ld, int q_off, int k
                             long long v_slot_stride, int M, int H, int G, int dim, int vdim, lia_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LIA_CHECK_ARG(y && meta && q_out && kcache && vcache, "lia_qkv_prep: null pointer");
-  LIA_CHECK_ARG(M > 0 && H > 0 && G > 0 && dim > 0 && vdim > 0 && taps >= 1 && taps <= 8 && (taps == 1 || (wconv && conv_state)),
+  LIA_CHECK_ARG(M > 0 && H > 0 && G > 0 && dim > 0 && vdim > 0 && taps >= 1 && taps <= 16 && (taps == 1 || (wconv && conv_state)),
                 "lia_qkv_prep: bad shape H=%d G=%d dim=%d vdim=%d taps=%d", H, G, dim, vdim, taps);
   LIA_CHECK_ARG(norm_mode >= 0 && norm_mode <= 2 && (norm_mode == 0 || (qnorm_w && knorm_w)), "lia_qkv_prep: bad norm mode %d", norm_mode);
   LIA_CHECK_ARG(rot_dims >= 0 && rot_dims <= dim && rot_dims % 2 == 0 && (rot_dims == 0 || freq), "lia_qkv_prep: cannot rotate %d of %d channels", rot_dims, dim);

@@ -127,6 +127,16 @@ def distance_slopes(heads):
     return [2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)]
 
 
+class _Prefixed:
+    """``w[name]`` -> the checkpoint's tensor ``prefix + name``, read when it is asked for."""
+
+    def __init__(self, fetch, prefix):
+        self.fetch, self.prefix = fetch, prefix
+
+    def __getitem__(self, name):
+        return self.fetch(self.prefix + name)
+
+
 class _Layer:
     def __init__(self, mixer, mlp, norm1, norm2, rg1_b, rg2, rg2_b, dwa):
         self.mixer, self.mlp, self.norm1, self.norm2 = mixer, mlp, norm1, norm2
@@ -168,7 +178,7 @@ class BizetarForCausalLM:
         self.layers = []
         for i, l in enumerate(cfg.layers):
             p, m = f"l{i}.", l["mixer"]
-            w = {k[len(p) + 4:]: fetch(k) for k in shapes if k.startswith(p + "mix.")}
+            w = _Prefixed(fetch, p + "mix.")              # the mixer asks for the tensors its options need, and no others
             v_mix = None if not m.get("v_mix") else ("publish" if i == first_mix else "blend")
             common = dict(norm_eps=cfg.norm_eps, dtype=dt, device=dev, v_mix=v_mix, ride_along=[fetch(p + "rg1")])
             if l["type"] == "attention":
@@ -265,7 +275,7 @@ class BizetarForCausalLM:
                 extras = []
                 if layer.rg2 is not None:
                     extras.append(layer.rg2(h))
-                    y = layer.mlp(h)
+                    y = layer.mlp(h, router_input=x)             # the router reads the fp32 stream itself
                 else:
                     y = layer.mlp(h, extras)
                 ops.gated_rms_add(x, y, layer.norm2, h, eps, gate=extras[0], gate_bias=layer.rg2_b, **last)

@@ -512,11 +512,13 @@ class MoEFeedForward:
                         identity=(idx, E, h, wt) if self.identity else None)
         return y
 
-    def __call__(self, h):
+    def __call__(self, h, router_input=None):
+        """``router_input``: the same rows before they were rounded to the activations' dtype (the fp32 residual stream), for
+        router logits that do not see that rounding; None: the router reads ``h``."""
         M, W, dev = h.shape[0], h.shape[1], h.device
         R, top = self.R, self.top
         logits = torch.empty(M, R, dtype=F32, device=dev)
-        ops.linear_small(h, self.router, None, logits, ops.GATE_NONE)
+        ops.linear_small(h if router_input is None else router_input, self.router, None, logits, ops.GATE_NONE)
         idx = torch.empty(M, top, dtype=torch.int32, device=dev)
         wt = torch.empty(M, top, dtype=F32, device=dev)
         ops.router_topk(logits, top, idx, wt, correction=self.correction, renorm=self.renorm)
