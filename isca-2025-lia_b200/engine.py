@@ -125,16 +125,23 @@ class Engine:
         """entries: dicts ``{"id", "tokens", "want"}``; returns fp32 logits [wanted places, vocab] in the order of the entries
         and of their ``want`` lists (None if nothing is wanted)."""
         vocab = self.model.config.vocab
-        todo = []
+        todo, restore = [], []
         for e in entries:
             toks = [int(t) for t in e["tokens"]]
             if not toks:
                 continue
             if min(toks) < 0 or max(toks) >= vocab:
                 raise ValueError(f"request {e['id']!r}: token id outside [0, {vocab})")
-            want = sorted(int(w) for w in e.get("want", ()))
-            if want and (want[0] < 0 or want[-1] >= len(toks)):
+            given = [int(w) for w in e.get("want", ())]
+            if given and (min(given) < 0 or max(given) >= len(toks)):
                 raise ValueError(f"request {e['id']!r}: wanted place outside its {len(toks)} tokens")
+            # the passes produce an entry's rows in ascending order of place; `restore` puts them back into the order asked for
+            order = sorted(range(len(given)), key=given.__getitem__)
+            want = [given[i] for i in order]
+            at = len(restore)
+            restore += [0] * len(given)
+            for r, g in enumerate(order):
+                restore[at + g] = at + r
             slot = self.slots.slot_of(e["id"])
             if slot is None:
                 slot = self.slots.alloc(e["id"])
@@ -162,7 +169,10 @@ class Engine:
                 self.slots.free(rid)
         if not outs:
             return None
-        return outs[0] if len(outs) == 1 else torch.cat(outs, 0)
+        logits = outs[0] if len(outs) == 1 else torch.cat(outs, 0)
+        if restore != list(range(len(restore))):
+            logits = logits[torch.tensor(restore, dtype=torch.int64, device=logits.device)]
+        return logits
 
     def generate(self, prompts, max_new_tokens, chunk=None, suppress_id=-1):
         """Greedy decoding of ``prompts`` (lists of ids, any lengths) as one batch: prompts in portions of ``chunk`` tokens

@@ -123,3 +123,32 @@ def test_oracle_router_and_identity_experts():
     idx, wt = O.route(h, wr, w["correction"], 2)
     assert bool((idx >= 1).all())
     assert torch.allclose(O.moe(h, w, "", cfg), wt.sum(-1, keepdim=True) * h)              # identity experts only: the token, weighted
+
+
+class _RowEcho:
+    """Stands in for a model: the logits of a wanted row are its token id in every column."""
+
+    class config:
+        vocab = 50
+
+    device = torch.device("cpu")
+
+    def new_state(self, n, cap):
+        from lia_b200.seq_state import SlotState
+        return SlotState(n, cap, "cpu")
+
+    def forward_rows(self, ids, batch, want, slots, trace=None):
+        return None if want is None else ids[want.long()].float()[:, None].expand(-1, 50).contiguous()
+
+    def graph_class(self, max_ctx):
+        return 0
+
+
+def test_engine_returns_wanted_places_in_the_order_asked_for():
+    """Places that are not ascending, a place asked for twice, an entry that is cut into several passes, two entries."""
+    from lia_b200.engine import Engine
+    e = Engine(_RowEcho(), max_tokens=64, max_requests=2, max_rows=4)
+    out = e.step([{"id": "x", "tokens": [10, 11, 12, 13, 14, 15, 16], "want": [6, 0, 3, 3, 5]}, {"id": "y", "tokens": [20, 21, 22], "want": [2, 1]}])
+    assert out[:, 0].tolist() == [16, 10, 13, 13, 15, 22, 21]
+    out = e.step([{"id": "x", "tokens": [30, 31], "want": [0, 1]}, {"id": "y", "tokens": [40], "want": []}])
+    assert out[:, 0].tolist() == [30, 31]
