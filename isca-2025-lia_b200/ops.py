@@ -706,7 +706,7 @@ def window_attn_plan(M, nseg, H, G, dim, vdim, window, max_ctx, sms):
         hb = ng * rep
     qr = 1 if M < 2 * nseg else max(1, 8 * lib.lia_window_attn_pairs_per_warp(vdim) // hb)
     blocks = (M + qr - 1) // qr * ((H + hb - 1) // hb)
-    want = (2 * sms + blocks - 1) // blocks
+    want = max(1, 2 * sms // blocks)          # two blocks fit an SM: as many key ranges as keep all blocks in ONE wave
     nsplit = max(1, min(want, window_attn_split_class(max_ctx, window))) if qr == 1 and max_ctx > 0 else 1
     return hb, qr, nsplit
 
