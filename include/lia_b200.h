@@ -405,14 +405,14 @@ int lia_window_attn_ext(const void* q, int ldq, int q_f32, int act_f32, const vo
 /* What turns the q | k | v columns of a projection's output y (row stride ld) into attention inputs, per token row with
  * meta[row] = {slot, position}; each step is optional and they come in this order:
  *   bias [H*dim + G*dim + G*vdim] added;
- *   a short causal convolution over time per channel (taps <= 16, wconv [channels][taps], last column = current token; the
+ *   a short causal convolution along the sequence, channel by channel (taps <= 16, wconv [channels][taps], last column = current token; the
  *   taps - 1 outputs of the projection before a portion come from conv_state [slot][taps-1][channels] fp32, kept current by
  *   lia_conv_state_update; what lies before the sequence's start is zero);
  *   RMS norm of q and of k -- norm_mode 1: over the whole projection, weights [H*dim] and [G*dim]; 2: per head, weights [dim];
  *   q times 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1) (temp_every > 0);
  *   rotation of the first rot_dims channels of every q and k head by pos * freq[i] (freq: rot_dims/2 doubles), pairs
  *   (2i, 2i+1), or (i, i + rot_dims/2) if rot_halves != 0; cos and sin times rot_mag;
- *   values -- vmix_mode 1: copied to v_first [M][G*vdim] fp32; 2: v = (1 - lambda) v + lambda v_first.
+ *   values -- vmix_mode 1: copied to v_first [M][G*vdim] fp32; 2: v moves towards v_first by the fraction lambda, v += lambda (v_first - v).
  * q goes to q_out [M][H*dim] fp32, k and v to the caches [slot][capacity][G*dim | G*vdim] of the activations' type. */
 int lia_qkv_prep(const void* y, int act_f32, int ld, int q_off, int k_off, int v_off, const float* bias, const float* wconv,
                  const float* conv_state, int taps, int norm_mode, const float* qnorm_w, const float* knorm_w, float eps, float temp_coef,
@@ -427,8 +427,8 @@ int lia_qkv_prep(const void* y, int act_f32, int ld, int q_off, int k_off, int v
 int lia_gated_rms_add(float* x, const void* y, int y_f32, const void* r, int ldr, const float* rb, const float* w, float* stack,
                       long long stack_stride, int n_mix, const float* mix, void* h, int act_f32, int rows, int W, float eps,
                       lia_stream_t stream);
-/* out[m] = a N(z) + b N(z^2) + c N(z^3) + e over z = in[m][:F] (row stride ld), powers element by element,
- * N(u) = u / sqrt(mean(u^2) + eps); coef = {a, b, c, e} fp32 on the device */
+/* out[m] = k1 R(z) + k2 R(z*z) + k3 R(z*z*z) + k0 over z = in[m][:F] (row stride ld), products element by element,
+ * R(u) = u / sqrt(mean(u^2) + eps); coef = {k1, k2, k3, k0} fp32 on the device */
 int lia_poly_norm(const void* in, int ld, const float* coef, void* out, int act_f32, int M, int F, float eps, lia_stream_t stream);
 
 #ifdef __cplusplus

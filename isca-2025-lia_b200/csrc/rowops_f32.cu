@@ -128,8 +128,8 @@ __global__ void __launch_bounds__(256) gated_rms_add_kernel(float* __restrict__ 
   }
 }
 
-// out = a N(z) + b N(z^2) + c N(z^3) + e, powers taken element by element, N(u) = u / sqrt(mean(u^2) + eps) over the row
-// of F numbers; coef = {a, b, c, e} on the device.  Block per row: one pass for the three sums of squares, one for the output.
+// out = k1 R(z) + k2 R(z*z) + k3 R(z*z*z) + k0, products element by element, R(u) = u / sqrt(mean(u^2) + eps) over the row
+// of F numbers; coef = {k1, k2, k3, k0} on the device.  Block per row: one pass for the three sums of squares, one for the output.
 template <typename T>
 __global__ void __launch_bounds__(256) poly_norm_kernel(const T* __restrict__ in, int ld, const float* __restrict__ coef, T* __restrict__ out, int F,
                                                         float eps) {

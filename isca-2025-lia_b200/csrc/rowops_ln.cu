@@ -134,8 +134,8 @@ __global__ void gated_act_kernel(const T* __restrict__ in, int ld, int up_off, T
 
 // ---------------------------------------------------------------------------------------------------- router
 // One warp per token: softmax over E logits (fp32), then `top` rounds of arg-max (lowest index on ties) over the scores
-// plus an optional per-expert correction that takes part in the choice only; the weights are the chosen experts' plain
-// scores, divided by their sum (+ 1e-20) when `renorm` is set.
+// plus an optional per-expert correction that takes part in the choice only; a chosen expert's weight is its plain
+// score, divided by their sum (+ 1e-20) when `renorm` is set.
 __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int* __restrict__ idx,
                                                           float* __restrict__ wt, int M, int E, int top, int renorm) {
   extern __shared__ float sc[];          // [4 warps][2][E]: scores, choice scores

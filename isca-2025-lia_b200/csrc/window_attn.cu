@@ -8,15 +8,15 @@
 //   window_attn:  one block per (group of token rows, group of up to 8 query heads, range of keys); a warp owns (row, head)
 //                 pairs.  32 cached positions at a time are staged in shared memory as fp32 for the key/value heads the
 //                 block's query heads use, once for all rows of the block that continue one sequence; lane j scores key j,
-//                     s = cap * tanh((q . k) * scale * temp_h / cap) - slope_h * (pos - j)     (cap <= 0: no cap)
+//                     s = cap * tanh((q . k) * scale * temp_h / cap) - slopes[h] * (pos - j)     (cap <= 0: no cap)
 //                 over the positions j with 0 <= pos - j < window, folds the stage into a running softmax and accumulates the
-//                 values (lane l owns channels l, l + 32, ...).  With a sink the denominator also holds exp(sink_h), a term
+//                 values (lane l owns channels l, l + 32, ...).  A sink adds exp(sink[h]) to the softmax's denominator, a term
 //                 without key or value.  The output can be multiplied by a gate, one number per (row, head) or sigmoid of
 //                 one pre-activation per channel.  Scores, weights and sums are fp32; the queries may be fp32 while the
 //                 caches are bf16.  Few rows and a long window (decoding): the keys are split over several blocks and a
 //                 second kernel combines.
 //   qkv_prep:     what turns a projection's q | k | v columns into attention inputs, per token: bias, a short causal
-//                 convolution over time per channel, an RMS norm of q and of k (over the whole projection or per head), a
+//                 convolution along the sequence per channel, an RMS norm of q and of k (over the whole projection or per head), a
 //                 position-dependent query temperature, a rotation of channel pairs, a blend of the values with the values
 //                 that an earlier layer published for the same token; q goes out in fp32, k and v into the caches.
 #include <math.h>
@@ -67,7 +67,7 @@ struct PrepArgs {
   int norm_mode;                 // 0 none; 1 one RMS norm over all of q (and all of k), weights [H*dim], [G*dim]; 2 per head, weights [dim]
   int temp_every;                // > 0: q *= 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)
   int rot_dims, rot_halves;      // channels (2i, 2i+1), i < rot_dims/2, of every head turn by pos * freq[i]; rot_halves != 0: pairs (i, i + rot_dims/2)
-  int vmix_mode;                 // 0 none; 1 publish v into v_first; 2 v = (1 - lambda) v + lambda v_first
+  int vmix_mode;                 // 0 none; 1 publish v into v_first; 2 v += lambda (v_first - v)
   float eps, temp_coef, rot_mag, lambda;
 };
 
@@ -186,7 +186,7 @@ struct WindowArgs {
 // what the scores and the output take besides q, k, v (each may be null)
 struct WindowExtras {
   const float* temp;     // [H] multiplies the scaled score
-  const float* slopes;   // [H] slope_h * (pos - j) is taken off the score
+  const float* slopes;   // [H] slopes[h] * (pos - j) is taken off the score
   const float* sink;     // [H] exp(sink_h) joins the softmax's denominator
   const void* gate;      // see WindowArgs::gate_mode
 };

@@ -11,7 +11,8 @@ Two mixers, both causal softmax attention over the whole history with grouped ke
 softmax's denominator (``seq_layers.SinkAttentionMixer`` with different options):
   ``attention``    one RMS norm over the whole query projection and one over the whole key projection, a query temperature
                    that grows with the logarithm of the position, no rotation but a per-head distance bias
-                   slope_h (i - j), slope_h = 2^(-8 (h + 1) / H), and one output gate per head;
+                   (head n of H, counted from 1, takes 2^(-8n/H) off a score per position between query and key), and one
+                   output gate per head;
   ``attention_2``  projections with biases behind a short causal convolution, a norm per head, rotated channel pairs with
                    interpolated frequencies, and one output gate per channel.
 Layers that say ``v_mix`` blend their values with those of the first such layer (same token) before caching them.
@@ -123,7 +124,7 @@ class BizetarConfig:
 
 
 def distance_slopes(heads):
-    """slope_h = 2^(-8 (h + 1) / H): what each head takes off a score per position of distance."""
+    """What each head takes off a score per position of distance: head n of H, counted from 1, takes 2^(-8n/H)."""
     return [2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)]
 
 

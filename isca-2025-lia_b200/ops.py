@@ -817,7 +817,7 @@ def gated_rms_add(x, y, w, h, eps, gate=None, gate_bias=None, stack=None, n_mix=
 
 
 def poly_norm(inp, F, coef, out, eps):
-    """out = a N(z) + b N(z^2) + c N(z^3) + e over z = inp[:, :F], N = division by the row's root mean square; coef fp32 [4]."""
+    """out = k1 R(z) + k2 R(z*z) + k3 R(z*z*z) + k0 over z = inp[:, :F], R = division by the row's root mean square; coef = (k1, k2, k3, k0) fp32."""
     ld = _rowmajor(inp, "inp")
     M = inp.shape[0]
     if tuple(out.shape) != (M, F) or not out.is_contiguous() or out.dtype != inp.dtype or _req(coef, "coef", F32).numel() != 4:

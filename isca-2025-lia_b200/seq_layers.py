@@ -285,7 +285,7 @@ def scaled_rotary_freq(dims, base, scaling=None):
     """Rotation frequencies f_i = base^(-2i/dims), i < dims/2, as float64, and the factor on cos and sin.  With ``scaling``
     {factor, original, fast, slow} (the "YaRN" interpolation): pairs that turn more than ``fast`` times within ``original``
     positions keep f_i, those that turn fewer than ``slow`` times get f_i / factor, the ones between are blended linearly in
-    the pair index, and cos and sin are multiplied by 0.1 ln(factor) + 1."""
+    the pair index, and the rotation's amplitude becomes 1 + 0.1 ln(factor)."""
     import math
     i = torch.arange(dims // 2, dtype=torch.float64)
     f = float(base) ** (-2.0 * i / dims)
@@ -307,13 +307,13 @@ class SinkAttentionMixer:
     softmax's denominator (a term without key or value).  Everything else is an option, so that designs which differ in them
     share the mixer:
       ``biases``   q, k, v projections with biases ("q.b", ...);
-      ``taps``     a short causal convolution over time on every channel of q, k, v right after the projection ("q.conv"
+      ``taps``     a short causal convolution along the sequence on every channel of q, k, v right after the projection ("q.conv"
                    [channels, taps], ...; None: no convolution); the last taps - 1 projected rows are per-sequence state;
       ``norm``     "whole": one RMS norm over all of q and one over all of k ("q.norm" [H*dim], "k.norm" [G*dim]);
                    "head": per head with a weight [dim] shared by the heads;
       ``q_temp``   (coef, every): q times 1 + coef * ln(floor((pos + 1) / every) + 1);
       ``rot``      {"dims", "base", "scaling"}: the first ``dims`` channels of every q and k head turn in pairs (2i, 2i+1);
-      ``slopes``   [H]: slope_h * (i - j) is taken off the score of query i and key j;
+      ``slopes``   [H]: every position between query and key costs head h slopes[h] of the score;
       ``v_mix``    "publish": this layer's values are left in the step's scratch for later layers; "blend": v becomes
                    (1 - vmix) v + vmix v_published before it is cached;
       ``gate``     "head": head h's output times sigmoid(Wg h)_h; "channel": the concatenated heads times sigmoid(Wg h);
@@ -398,8 +398,8 @@ class SinkAttentionMixer:
 
 
 class PolyNormMLP:
-    """Wdown act(Wup h) with the polynomial activation between norms: act(z) = a N(z) + b N(z^2) + c N(z^3) + e, powers taken
-    element by element, N = division of a token's ff numbers by their root mean square (fp32).  ``ride_along``: further weight
+    """Wdown act(Wup h) with the polynomial activation between norms: act(z) = k1 R(z) + k2 R(z*z) + k3 R(z*z*z) + k0, products taken
+    element by element, R = division of a token's ff numbers by their root mean square (fp32).  ``ride_along``: further weight
     matrices that read the same input and join the up projection (outputs appended to ``extras``)."""
 
     def __init__(self, w, ff, norm_eps, dtype, device, ride_along=()):

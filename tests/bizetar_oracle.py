@@ -26,7 +26,7 @@ def silu(z):
 
 
 def poly_norm(z, coef, eps):
-    """a N(z) + b N(z^2) + c N(z^3) + e with N = division by the row's root mean square."""
+    """k1 R(z) + k2 R(z*z) + k3 R(z*z*z) + k0 with R = division by the row's root mean square; coef = (k1, k2, k3, k0)."""
     a, b, c, e = (float(t) for t in coef)
     return a * rms_div(z, eps) + b * rms_div(z * z, eps) + c * rms_div(z * z * z, eps) + e
 
@@ -108,7 +108,7 @@ def rotate_pairs(x, cos, sin, dims):
 
 def sink_attention(q, k, v, pos, scale, sink, slopes=None):
     """q [T, H, d] at positions pos [T]; k [N, G, d], v [N, G, e]: the whole history, key j at position j.  Softmax over the
-    visible keys plus one sink term exp(sink_h) that has no value; an optional distance bias slope_h * (i - j) is taken off."""
+    visible keys plus one sink term exp(sink_h) that has no value; optionally every position of distance costs head h slopes[h] of the score."""
     T, H, _ = q.shape
     N, G = k.shape[0], k.shape[1]
     out = torch.zeros(T, H, v.shape[-1], dtype=F64)
