@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define LIA_ABI_VERSION 8
+#define LIA_ABI_VERSION 9
 
 typedef void* lia_stream_t; /* cudaStream_t */
 
@@ -306,7 +306,8 @@ int lia_latent_attn(const float* qa, const void* cache, int cache_f32, long long
  * recurrences (a fixed decay per head, or the gated delta rule behind a short convolution), sliding-window attention
  * with grouped key/value heads, and dense or mixture-of-experts feed-forwards.  Same conventions as the section above.
  * The reference has none of these. */
-enum { LIA_ACT_NONE = 0, LIA_ACT_RELU = 1, LIA_ACT_SILU = 2, LIA_ACT_GELU_ERF = 3, LIA_ACT_GELU_TANH = 4 };
+enum { LIA_ACT_NONE = 0, LIA_ACT_RELU = 1, LIA_ACT_SILU = 2, LIA_ACT_GELU_ERF = 3, LIA_ACT_GELU_TANH = 4,
+       LIA_ACT_CLAMPED_SWISH = 5 /* gated form only: see lia_moe_gemm_act */ };
 
 /* x[r] = table[ids[r]] as fp32; x_copy (may be NULL) receives the same rows */
 int lia_embed_rows(const int64_t* ids, const void* table, int table_f32, float* x, float* x_copy, int rows, int W, int vocab,
@@ -430,6 +431,58 @@ int lia_gated_rms_add(float* x, const void* y, int y_f32, const void* r, int ldr
 /* out[m] = k1 R(z) + k2 R(z*z) + k3 R(z*z*z) + k0 over z = in[m][:F] (row stride ld), products element by element,
  * R(u) = u / sqrt(mean(u^2) + eps); coef = {k1, k2, k3, k0} fp32 on the device */
 int lia_poly_norm(const void* in, int ld, const float* coef, void* out, int act_f32, int M, int F, float eps, lia_stream_t stream);
+
+/* ---- Pre-norm designs with learned positions: latent attention with latent queries and a pairwise rotation, several attention
+ * maps over shared values under a chunked mask, a forget-gate recurrence, experts with a clamped gated activation.  (ABI 9) ---- */
+
+/* x[row] = table[ids[row]] * scale + pos_table[meta[row].position] in fp32 (pos_table may be NULL; the tables share a type).
+ * cat (may be NULL): [rows][2 W] of the given type receives the row twice, side by side. */
+int lia_embed_scale_pos(const int64_t* ids, const void* table, const void* pos_table, int table_f32, float scale, const int* meta, float* x,
+                        void* cat, int cat_f32, int rows, int W, int vocab, int max_pos, lia_stream_t stream);
+/* x = (replace ? 0 : x) + y + bias (y [rows][W], bias [W] fp32; each may be NULL), then h = w * x / sqrt(mean(x^2) + eps) in the
+ * activations' type with row stride ldh (w NULL: h = x; h NULL: no output).  x is the fp32 residual stream. */
+int lia_residual_norm(float* x, const void* y, int y_f32, int replace, const float* bias, const float* w, void* h, int h_f32, long long ldh,
+                      int rows, int W, float eps, lia_stream_t stream);
+/* out[m] = w * z / sqrt(mean(z^2) + eps), z = in[m][0..N) with row stride ld; out contiguous [M][N] */
+int lia_rms_norm_rows(const void* in, int in_f32, long long ld, const float* w, void* out, int out_f32, int M, int N, float eps,
+                      lia_stream_t stream);
+/* out = a * sigmoid(gate) over [M][F]; a and gate are row-major views; out contiguous, of the gate's type */
+int lia_sigmoid_mul(const void* a, int a_f32, long long lda, const void* gate, int gate_f32, long long ldg, void* out, int out_f32, int M, int F,
+                    lia_stream_t stream);
+/* x = cap * tanh(x / cap) in place over n numbers */
+int lia_softcap_f32(float* x, long long n, float cap, lia_stream_t stream);
+/* lia_moe_gemm_ext with the activation's parameters: LIA_ACT_CLAMPED_SWISH (gated up projection only) computes
+ * g' * sigmoid(p1 * g') * (u' + 1) with g' = min(g, p0), u' = clamp(u, -p0, p0) */
+int lia_moe_gemm_act(const void* A, int a_f32, int lda, const void* W, int w_f32, long long w_expert_stride, void* C, int c_f32, int ldc,
+                     const int* perm, const int* tile_expert, int n_tiles, const int* idx, const float* wt, int pairs, int top, int N, int K,
+                     int up, int act, int gated, int n_real, float act_p0, float act_p1, lia_stream_t stream);
+/* The q | f | v columns of a projection's output -> fp32 inputs of the forget-gate recurrence: out[row] = silu(q) | low + (1 - low) *
+ * sigmoid(f + f_bias) | v  (nq channels of q and of f, nv of v; f_bias may be NULL). */
+int lia_forget_gate_prep(const void* y, int y_f32, int ld, int q_off, int f_off, int v_off, const float* f_bias, const float* low, float* out,
+                         int M, int nq, int nv, lia_stream_t stream);
+/* per head and channel d: S[d][:] <- f[d] S[d][:] + (1 - f[d]) v, then o = sum_d q[d] S[d][:], over every portion; state_S [slot][H][vdim][dim] fp32 (lia_linear_scan's layout) */
+int lia_forget_scan(const float* q, const float* f, int ldqf, const float* v, int ldv, float* state_S, const int* segs, int nseg, int H, int dim,
+                    int vdim, float* o, lia_stream_t stream);
+/* lia_window_attn_ext with: chunk > 0 -- a query at position p attends to keys [p - p % chunk, p] only; v_div -- key head g
+ * reads value head g / v_div (the value cache holds G / v_div heads); out_f32 -- fp32 output on caches of any type */
+int lia_window_attn_masked(const void* q, int ldq, int q_f32, int act_f32, const void* kcache, long long k_slot_stride, const void* vcache,
+                           long long v_slot_stride, const int* meta, const float* temp, const float* slopes, const float* sink, const void* gate,
+                           int gate_mode, int ldg, void* out, int out_f32, float* workspace, int M, int H, int G, int v_div, int dim, int vdim,
+                           int window, int chunk, float scale, float softcap, int heads_per_block, int rows_per_block, int nsplit,
+                           lia_stream_t stream);
+/* lia_qkv_prep with Gv value heads beside G key heads */
+int lia_qkv_prep_heads(const void* y, int act_f32, int ld, int q_off, int k_off, int v_off, const float* bias, const float* wconv,
+                       const float* conv_state, int taps, int norm_mode, const float* qnorm_w, const float* knorm_w, float eps, float temp_coef,
+                       int temp_every, const double* freq, int rot_dims, int rot_halves, float rot_mag, int vmix_mode, float lambda, float* v_first,
+                       const int* meta, float* q_out, void* kcache, long long k_slot_stride, void* vcache, long long v_slot_stride, int M, int H,
+                       int G, int Gv, int dim, int vdim, lia_stream_t stream);
+/* a [M][G][2][H/G][vdim] fp32 (two attention maps per head) -> out [M][H][vdim]: o = a1 - lambda a2, out = mult * o / sqrt(mean(o^2) + eps) */
+int lia_diff_combine(const float* a, void* out, int act_f32, int M, int H, int G, int vdim, float lambda, float mult, float eps,
+                     lia_stream_t stream);
+/* lia_latent_prep with the rotation of channel pairs (2i, 2i+1) by pos * freq[i] (rot_dims/2 doubles) and the amplitude mag */
+int lia_latent_prep_pairs(const void* q, int ldq, const void* dkv, int ldd, int act_f32, const float* c_norm_w, const double* freq, float mag,
+                          const int* meta, void* cache, long long slot_stride, float* qa, int M, int H, int dim, int rot, int rot_dims,
+                          int kv_rank, float eps, lia_stream_t stream);
 
 #ifdef __cplusplus
 }

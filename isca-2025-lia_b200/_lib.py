@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libliab200.so")
 
 EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_RESIDUAL, EPI_QKV = 0, 1, 2, 3
-ABI_VERSION = 8
+ABI_VERSION = 9
 TP_MAX_WORLD = 8
 P2P_HANDLE_BYTES = 64
 
@@ -145,6 +145,27 @@ _PROTOTYPES = {
                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "lia_moe_combine_ext": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                     c_int, c_void_p]),
+    # pre-norm designs with learned positions: latent queries, pairwise rotation, attention maps over shared values under a
+    # chunked mask, the forget-gate recurrence, experts with a clamped gated activation
+    "lia_embed_scale_pos": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                    c_void_p]),
+    "lia_residual_norm": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_float, c_void_p]),
+    "lia_rms_norm_rows": (c_int, [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]),
+    "lia_sigmoid_mul": (c_int, [c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "lia_softcap_f32": (c_int, [c_void_p, c_longlong, c_float, c_void_p]),
+    "lia_moe_gemm_act": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
+                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p]),
+    "lia_forget_gate_prep": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "lia_forget_scan": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "lia_window_attn_masked": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                       c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_void_p]),
+    "lia_qkv_prep_heads": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                   c_float, c_float, c_int, c_void_p, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "lia_diff_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p]),
+    "lia_latent_prep_pairs": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_longlong, c_void_p,
+                                      c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
 }
 
 EXPORTS = tuple(_PROTOTYPES)

@@ -9,6 +9,8 @@
 //   latent_prep:  RMS-norm of the latent part with its per-channel weight, rotary embedding ("rotate half": channel i is
 //                 paired with i + dims/2) of the shared key part at the token's position, both written into the cache row;
 //                 the same rotation of each head's rotated query part, written behind that head's q~ slot.
+//                 latent_prep_pairs is the same step with the rotation of neighbouring channels (2i, 2i+1) by angles from a
+//                 float64 frequency table (so that interpolated frequencies come from the host) and an amplitude on cos and sin.
 //   latent_attn:  one block per (token, group of up to 8 heads, range of keys); 32 cached rows at a time are staged in shared
 //                 memory as fp32, scored (warp = head, lane = key), folded into a running softmax, and accumulated.  Few rows
 //                 and a long history (decoding): the keys are split over several blocks and a second kernel combines.
@@ -68,6 +70,52 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(const T* __restrict__ 
     for (int i = threadIdx.x; i < rot; i += 128) sh[i] = ldf(qin + (size_t)row * ldq + h * (dim + rot) + dim + i);
     __syncthreads();
     for (int i = threadIdx.x; i < rot; i += 128) qa[((size_t)row * H + h) * D + kv_rank + i] = rotate_half(sh, i, rot_dims, pos, inv_freq);
+  }
+}
+
+// The same step with the pairwise rotation: channels (2i, 2i+1), i < rot_dims/2, turn by pos * freq[i]; cos and sin carry the
+// amplitude `mag`.  The angle is a float64 product (positions in the thousands times an irrational frequency), its sine and
+// cosine are rounded once to fp32 and shared by the key part and all heads' query parts.
+template <typename T>
+__global__ void __launch_bounds__(128) latent_prep_pairs_kernel(const T* __restrict__ qin, int ldq, const T* __restrict__ dkv, int ldd,
+                                                                const float* __restrict__ cw, const double* __restrict__ freq, float mag,
+                                                                const int* __restrict__ meta, T* __restrict__ cache, long long slot_stride,
+                                                                float* __restrict__ qa, int H, int dim, int rot, int rot_dims, int kv_rank, float eps) {
+  extern __shared__ float cs[];                 // cos | sin of the rot_dims / 2 pairs
+  __shared__ float red[4];
+  const int row = blockIdx.x;
+  const int slot = meta[2 * row], p = meta[2 * row + 1];
+  const int D = kv_rank + rot, npair = rot_dims / 2;
+  const T* d = dkv + (size_t)row * ldd;
+  T* crow = cache + (size_t)slot * slot_stride + (size_t)p * D;
+  for (int i = threadIdx.x; i < npair; i += 128) {
+    double sn, c;
+    sincos((double)p * freq[i], &sn, &c);
+    cs[i] = (float)c * mag;
+    cs[npair + i] = (float)sn * mag;
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < kv_rank; i += 128) {
+    const float v = ldf(d + i);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  const float inv = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)kv_rank + eps);
+  for (int i = threadIdx.x; i < kv_rank; i += 128) stf(crow + i, ldf(d + i) * inv * cw[i]);
+  // vector 0: the shared key part (into the cache); vector 1 + h: head h's rotated query part (into its q~ slot, fp32)
+  for (int e = threadIdx.x; e < (H + 1) * rot; e += 128) {
+    const int vec = e / rot, i = e - vec * rot;
+    const T* src = vec == 0 ? d + kv_rank : qin + (size_t)row * ldq + (size_t)(vec - 1) * (dim + rot) + dim;
+    float val = ldf(src + i);
+    if (i < rot_dims) {
+      const float other = ldf(src + (i ^ 1));
+      const int pr = i >> 1;
+      val = (i & 1) == 0 ? val * cs[pr] - other * cs[npair + pr] : val * cs[pr] + other * cs[npair + pr];
+    }
+    if (vec == 0) stf(crow + kv_rank + i, val);
+    else qa[((size_t)row * H + (vec - 1)) * D + kv_rank + i] = val;
   }
 }
 
@@ -305,6 +353,24 @@ extern "C" int lia_latent_prep(const void* q, int ldq, const void* dkv, int ldd,
   else
     latent_prep_kernel<bf16><<<M, 128, smem, stream>>>(reinterpret_cast<const bf16*>(q), ldq, reinterpret_cast<const bf16*>(dkv), ldd, c_norm_w, inv_freq,
                                                        meta, reinterpret_cast<bf16*>(cache), slot_stride, qa, H, dim, rot, rot_dims, kv_rank, eps);
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+extern "C" int lia_latent_prep_pairs(const void* q, int ldq, const void* dkv, int ldd, int act_f32, const float* c_norm_w, const double* freq,
+                                     float mag, const int* meta, void* cache, long long slot_stride, float* qa, int M, int H, int dim, int rot,
+                                     int rot_dims, int kv_rank, float eps, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(q && dkv && c_norm_w && meta && cache && qa && (freq || rot_dims == 0), "lia_latent_prep_pairs: null pointer");
+  LIA_CHECK_ARG(M > 0 && H > 0 && dim >= 0 && rot > 0 && kv_rank > 0 && rot_dims >= 0 && rot_dims <= rot && rot_dims % 2 == 0 && rot <= 8192,
+                "lia_latent_prep_pairs: bad shape H=%d dim=%d rot=%d rot_dims=%d kv_rank=%d", H, dim, rot, rot_dims, kv_rank);
+  const size_t smem = (size_t)(rot_dims > 0 ? rot_dims : 2) * sizeof(float);
+  if (act_f32)
+    latent_prep_pairs_kernel<float><<<M, 128, smem, stream>>>(reinterpret_cast<const float*>(q), ldq, reinterpret_cast<const float*>(dkv), ldd, c_norm_w,
+                                                              freq, mag, meta, reinterpret_cast<float*>(cache), slot_stride, qa, H, dim, rot, rot_dims, kv_rank, eps);
+  else
+    latent_prep_pairs_kernel<bf16><<<M, 128, smem, stream>>>(reinterpret_cast<const bf16*>(q), ldq, reinterpret_cast<const bf16*>(dkv), ldd, c_norm_w,
+                                                             freq, mag, meta, reinterpret_cast<bf16*>(cache), slot_stride, qa, H, dim, rot, rot_dims, kv_rank, eps);
   LIA_LAUNCH_CHECK();
   return LIA_OK;
 }

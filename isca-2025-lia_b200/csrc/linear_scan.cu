@@ -3,6 +3,8 @@
 //
 //   DECAY  (a fixed decay per head):     S_t = d_h S_{t-1} + k_t v_t^T                      o_t = S_t^T q_t
 //   DELTA  (gated delta rule):           S'  = g_t S_{t-1};  u_t = beta_t (v_t - S'^T k_t);  S_t = S' + k_t u_t^T;  o_t = S_t^T q_t
+//   FORGET (keyless: the per-channel forget gate f_t keeps, its complement 1 - f_t writes):
+//                                        row d of S:  S[d] <- f[d] S[d] + (1 - f[d]) v      o = sum_d q[d] S[d]
 //
 // The state is fp32, one [vdim][dim] matrix per (slot, head) -- stored transposed so that the dim-long column a warp owns
 // is contiguous.  A warp keeps CW columns in registers for the whole portion, lane l owning rows l, l + 32, ...; a token
@@ -105,6 +107,33 @@ __global__ void __launch_bounds__(256) conv_state_update_kernel(const T* __restr
     if (i < taps - 1) st[(size_t)i * C + c] = keep[i];
 }
 
+// ---------------------------------------------------------------------------------------------------- forget gates
+// What turns the q | f | v columns of a projection's output (nq = H * dim channels of q and of f, nv of v) into the FORGET
+// recurrence's fp32 inputs, row by row:  q = silu(q),  f = low + (1 - low) * sigmoid(f + f_bias)  (low: the gate's lower
+// bound per channel),  v as it is;  out[row] = q | f | v.
+template <typename T>
+__global__ void forget_gate_prep_kernel(const T* __restrict__ y, int ld, int q_off, int f_off, int v_off, const float* __restrict__ f_bias,
+                                        const float* __restrict__ low, float* __restrict__ out, int M, int nq, int nv) {
+  const int C = 2 * nq + nv;
+  const size_t n = (size_t)M * C;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t m = e / C;
+    const int c = (int)(e - m * C);
+    const T* row = y + m * ld;
+    float val;
+    if (c < nq) {
+      val = silu(ldf(row + q_off + c));
+    } else if (c < 2 * nq) {
+      const int i = c - nq;
+      const float l = low[i];
+      val = l + (1.0f - l) / (1.0f + expf(-(ldf(row + f_off + i) + (f_bias ? f_bias[i] : 0.f))));
+    } else {
+      val = ldf(row + v_off + (c - 2 * nq));
+    }
+    out[e] = val;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------- the recurrence
 // Stage loads return RAW bits and nothing touches them until they are stored to shared memory, so all loads of a stage are
 // in flight together while the previous stage is processed.
@@ -158,11 +187,13 @@ constexpr int CB = CW * NW;      // columns per block
 
 // VL: the stage is fetched with 128-bit loads (the host checked that every q / k / v segment of VEC numbers starts on a
 // 16-byte boundary and lies wholly inside or outside its row).
-template <typename T, int DR, bool DELTA, bool VL>
+// MODE: 0 DECAY, 1 DELTA, 2 FORGET (the k slot of the stage carries f_t).
+template <typename T, int DR, int MODE, bool VL>
 __global__ void __launch_bounds__(NW * 32, 2) linear_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, int ldqk, const T* __restrict__ v, int ldv,
                                                               int in_silu, const float* __restrict__ decay, const float* __restrict__ gates,
                                                               float* __restrict__ St, const int* __restrict__ segs, int H, int G, int dim, int vdim,
                                                               float* __restrict__ o) {
+  constexpr bool DELTA = MODE == 1, FORGET = MODE == 2;
   constexpr int DP = DR * 32;                    // dim padded to whole warps
   constexpr int ROWF = 2 * DP + CB + 4;          // floats of one staged token: q | k | v (this block's columns) | beta | g | 2 pad
   constexpr int VEC = Vec128<T>::N;
@@ -183,7 +214,7 @@ __global__ void __launch_bounds__(NW * 32, 2) linear_scan_kernel(const T* __rest
 #pragma unroll
     for (int c = 0; c < CW; ++c) S[i][c] = (r < dim && col0 + c < vdim) ? Sp[(size_t)(col0 + c) * dim + r] : 0.f;
   }
-  const float dec = DELTA ? 0.f : decay[h];
+  const float dec = MODE == 0 ? decay[h] : 0.f;
 
   typename Raw<T>::type buf[VL ? 1 : NST];
   uint4 vbuf[VL ? NST : 1];
@@ -317,7 +348,8 @@ __global__ void __launch_bounds__(NW * 32, 2) linear_scan_kernel(const T* __rest
           const float qv = tk[lane + 32 * i], kv = tk[DP + lane + 32 * i];
 #pragma unroll
           for (int c = 0; c < CW; ++c) {
-            S[i][c] = fmaf(dec, S[i][c], kv * vc[c]);
+            if constexpr (FORGET) S[i][c] = fmaf(kv, S[i][c], (1.0f - kv) * vc[c]);     // kv is f_t here; padded rows stay unread
+            else S[i][c] = fmaf(dec, S[i][c], kv * vc[c]);
             out[c] = fmaf(S[i][c], qv, out[c]);
           }
         }
@@ -344,22 +376,25 @@ __global__ void __launch_bounds__(NW * 32, 2) linear_scan_kernel(const T* __rest
   }
 }
 
+template <typename T, int DR, int MODE, bool VL>
+int launch_scan_mode(const void* q, const void* k, int ldqk, const void* v, int ldv, int in_silu, const float* decay, const float* gates, float* St,
+                     const int* segs, int nseg, int H, int G, int dim, int vdim, float* o, cudaStream_t stream) {
+  const size_t smem = (size_t)2 * TB * (2 * DR * 32 + CB + 4) * sizeof(float);
+  dim3 grid((vdim + CB - 1) / CB, H, nseg);
+  if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(linear_scan_kernel<T, DR, MODE, VL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  linear_scan_kernel<T, DR, MODE, VL><<<grid, NW * 32, smem, stream>>>(reinterpret_cast<const T*>(q), reinterpret_cast<const T*>(k), ldqk,
+                                                                       reinterpret_cast<const T*>(v), ldv, in_silu, decay, gates, St, segs, H, G, dim, vdim, o);
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+// gates given: DELTA; decay given: DECAY; neither: FORGET
 template <typename T, int DR, bool VL>
 int launch_scan_as(const void* q, const void* k, int ldqk, const void* v, int ldv, int in_silu, const float* decay, const float* gates, float* St,
                    const int* segs, int nseg, int H, int G, int dim, int vdim, float* o, cudaStream_t stream) {
-  const size_t smem = (size_t)2 * TB * (2 * DR * 32 + CB + 4) * sizeof(float);
-  dim3 grid((vdim + CB - 1) / CB, H, nseg);
-  if (gates != nullptr) {
-    if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(linear_scan_kernel<T, DR, true, VL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    linear_scan_kernel<T, DR, true, VL><<<grid, NW * 32, smem, stream>>>(reinterpret_cast<const T*>(q), reinterpret_cast<const T*>(k), ldqk,
-                                                                        reinterpret_cast<const T*>(v), ldv, in_silu, decay, gates, St, segs, H, G, dim, vdim, o);
-  } else {
-    if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(linear_scan_kernel<T, DR, false, VL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    linear_scan_kernel<T, DR, false, VL><<<grid, NW * 32, smem, stream>>>(reinterpret_cast<const T*>(q), reinterpret_cast<const T*>(k), ldqk,
-                                                                         reinterpret_cast<const T*>(v), ldv, in_silu, decay, gates, St, segs, H, G, dim, vdim, o);
-  }
-  LIA_LAUNCH_CHECK();
-  return LIA_OK;
+  if (gates != nullptr) return launch_scan_mode<T, DR, 1, VL>(q, k, ldqk, v, ldv, in_silu, decay, gates, St, segs, nseg, H, G, dim, vdim, o, stream);
+  if (decay != nullptr) return launch_scan_mode<T, DR, 0, VL>(q, k, ldqk, v, ldv, in_silu, decay, gates, St, segs, nseg, H, G, dim, vdim, o, stream);
+  return launch_scan_mode<T, DR, 2, VL>(q, k, ldqk, v, ldv, in_silu, decay, gates, St, segs, nseg, H, G, dim, vdim, o, stream);
 }
 
 template <typename T, int DR>
@@ -427,4 +462,28 @@ extern "C" int lia_linear_scan(const void* q, const void* k, int ldqk, const voi
                 "lia_linear_scan: bad shape nseg=%d H=%d G=%d dim=%d vdim=%d", nseg, H, G, dim, vdim);
   if (act_f32) return dispatch_scan<float>(q, k, ldqk, v, ldv, in_silu, decay, gates, state_S, segs, nseg, H, G, dim, vdim, o, stream);
   return dispatch_scan<bf16>(q, k, ldqk, v, ldv, in_silu, decay, gates, state_S, segs, nseg, H, G, dim, vdim, o, stream);
+}
+
+extern "C" int lia_forget_gate_prep(const void* y, int y_f32, int ld, int q_off, int f_off, int v_off, const float* f_bias, const float* low,
+                                    float* out, int M, int nq, int nv, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(y && low && out && M > 0 && nq > 0 && nv > 0 && ld >= nq && q_off >= 0 && f_off >= 0 && v_off >= 0, "lia_forget_gate_prep: bad arguments");
+  const size_t n = (size_t)M * (2 * nq + nv);
+  size_t blocks = (n + 255) / 256;
+  const size_t capb = (size_t)lia_sm_count() * 16;
+  if (blocks > capb) blocks = capb;
+  if (y_f32) forget_gate_prep_kernel<float><<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(y), ld, q_off, f_off, v_off, f_bias, low, out, M, nq, nv);
+  else forget_gate_prep_kernel<bf16><<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const bf16*>(y), ld, q_off, f_off, v_off, f_bias, low, out, M, nq, nv);
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+// The FORGET recurrence: q, f fp32 column slices with one row stride (H heads of dim), v fp32 (H heads of vdim).
+extern "C" int lia_forget_scan(const float* q, const float* f, int ldqf, const float* v, int ldv, float* state_S, const int* segs, int nseg, int H,
+                               int dim, int vdim, float* o, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(q && f && v && state_S && segs && o, "lia_forget_scan: null pointer");
+  LIA_CHECK_ARG(nseg > 0 && nseg <= 65535 && H > 0 && H <= 65535 && dim > 0 && dim <= 512 && vdim > 0,
+                "lia_forget_scan: bad shape nseg=%d H=%d dim=%d vdim=%d", nseg, H, dim, vdim);
+  return dispatch_scan<float>(q, f, ldqf, v, ldv, 0, nullptr, nullptr, state_S, segs, nseg, H, H, dim, vdim, o, stream);
 }

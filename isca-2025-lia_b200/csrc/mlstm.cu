@@ -251,9 +251,13 @@ __global__ void __launch_bounds__(128) headnorm_gate_kernel(const float* __restr
   ss = warp_sum(ss);
   const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
   for (int c = lane; c < vdim; c += 32) {
-    const float g = ldf(gate + (size_t)row * ldg + h * vdim + c);
-    const float sg = 1.0f / (1.0f + expf(-g));
-    stf(out + (size_t)row * H * vdim + h * vdim + c, orow[c] * inv * w[h * vdim + c] * (gate_silu ? g * sg : sg));
+    float factor = 1.0f;                                    // no gate: the norm alone
+    if (gate != nullptr) {
+      const float g = ldf(gate + (size_t)row * ldg + h * vdim + c);
+      const float sg = 1.0f / (1.0f + expf(-g));
+      factor = gate_silu ? g * sg : sg;
+    }
+    stf(out + (size_t)row * H * vdim + h * vdim + c, orow[c] * inv * w[h * vdim + c] * factor);
   }
 }
 
@@ -304,7 +308,7 @@ extern "C" int lia_mlstm_scan(const void* q, const void* k, const void* v, int a
 extern "C" int lia_headnorm_gate(const float* o, const float* w, const void* gate, int ldg, void* out, int act_f32, int M, int H, int vdim,
                                  float eps, int gate_silu, lia_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  LIA_CHECK_ARG(o && w && gate && out && M > 0 && H > 0 && vdim > 0 && ldg >= H * vdim, "lia_headnorm_gate: bad arguments");
+  LIA_CHECK_ARG(o && w && out && M > 0 && H > 0 && vdim > 0 && (!gate || ldg >= H * vdim), "lia_headnorm_gate: bad arguments");
   const long long pairs = (long long)M * H;
   const unsigned grid = (unsigned)((pairs + 3) / 4);
   if (act_f32) headnorm_gate_kernel<float><<<grid, 128, 0, stream>>>(o, w, reinterpret_cast<const float*>(gate), ldg, reinterpret_cast<float*>(out), M, H, vdim, eps, gate_silu);

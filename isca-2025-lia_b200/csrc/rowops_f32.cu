@@ -86,6 +86,91 @@ __global__ void __launch_bounds__(256) rms_add_norm_kernel(float* __restrict__ x
   for (int i = threadIdx.x; i < W; i += 256) stf(h + base + i, xs[i] * inv * w_pre[w_pre_n == 1 ? 0 : i]);
 }
 
+// Pre-norm designs with learned positions and a per-channel norm weight:
+//   x[row] = table[ids[row]] * scale + pos_table[position of the row]          (fp32)
+//   cat (may be null): the row in the activations' type, twice side by side -- the pair [x ; x0] that a looped block's
+//   input projection reads (x0 stays the embedding, the left half is overwritten as the stream moves on).
+template <typename T, typename TC>
+__global__ void __launch_bounds__(256) embed_scale_pos_kernel(const int64_t* __restrict__ ids, const T* __restrict__ table, float scale,
+                                                              const T* __restrict__ pos_table, const int* __restrict__ meta, float* __restrict__ x,
+                                                              TC* __restrict__ cat, int W, int vocab, int max_pos) {
+  const int row = blockIdx.x;
+  long long id = ids[row];
+  if (id < 0 || id >= vocab) id = 0;     // the host checks the range; never read outside the table
+  int p = meta[2 * row + 1];
+  p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);      // the host refuses sequences longer than the table
+  const T* e = table + (size_t)id * W;
+  const T* pr = pos_table ? pos_table + (size_t)p * W : nullptr;
+  for (int i = threadIdx.x; i < W; i += 256) {
+    const float v = fmaf(ldf(e + i), scale, pr ? ldf(pr + i) : 0.f);
+    x[(size_t)row * W + i] = v;
+    if (cat != nullptr) {
+      stf(cat + (size_t)row * 2 * W + i, v);
+      stf(cat + (size_t)row * 2 * W + W + i, v);
+    }
+  }
+}
+
+// The residual update of pre-norm designs, fused with the norm (or the plain cast) that the next sublayer reads:
+//   x[row] = (replace ? 0 : x[row]) + y[row] + bias          (y, bias may be null; bias is one vector for all rows)
+//   h[row] = w * x / sqrt(mean(x^2) + eps)                   (w null: h = x), h in the activations' type with row stride ldh
+// `xs` (dynamic shared memory, W floats) keeps the updated row between the two.
+template <typename TY, typename TH>
+__global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ x, const TY* __restrict__ y, int replace, const float* __restrict__ bias,
+                                                            const float* __restrict__ w, TH* __restrict__ h, long long ldh, int W, float eps) {
+  extern __shared__ float xs[];
+  __shared__ float red[8];
+  const size_t base = (size_t)blockIdx.x * W;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < W; i += 256) {
+    float v = replace ? 0.f : x[base + i];
+    if (y != nullptr) v += ldf(y + base + i);
+    if (bias != nullptr) v += bias[i];
+    if (y != nullptr || bias != nullptr || replace) x[base + i] = v;
+    xs[i] = v;
+    ss += v * v;
+  }
+  if (h == nullptr) return;
+  float inv = 1.0f;
+  if (w != nullptr) {
+    ss = block_sum<256>(ss, red);
+    inv = 1.0f / sqrtf(ss / (float)W + eps);
+  }
+  for (int i = threadIdx.x; i < W; i += 256) stf(h + (size_t)blockIdx.x * ldh + i, w ? xs[i] * inv * w[i] : xs[i]);
+}
+
+// out[m] = w * z / sqrt(mean(z^2) + eps) over z = in[m][0..N) (a column slice with row stride ld); one warp per row
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(128) rms_norm_rows_kernel(const TI* __restrict__ in, long long ld, const float* __restrict__ w, TO* __restrict__ out,
+                                                            int M, int N, float eps) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const TI* z = in + (size_t)row * ld;
+  float ss = 0.f;
+  for (int i = lane; i < N; i += 32) {
+    const float v = ldf(z + i);
+    ss += v * v;
+  }
+  const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)N + eps);
+  for (int i = lane; i < N; i += 32) stf(out + (size_t)row * N + i, ldf(z + i) * inv * w[i]);
+}
+
+// out = a * sigmoid(g), element by element over [M][F]; a and g are row-major views with their own row strides
+template <typename TA, typename TG, typename TO>
+__global__ void sigmoid_mul_kernel(const TA* __restrict__ a, long long lda, const TG* __restrict__ g, long long ldg, TO* __restrict__ out, int M, int F) {
+  const size_t n = (size_t)M * F;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t m = e / F;
+    const int f = (int)(e - m * F);
+    stf(out + e, ldf(a + m * lda + f) / (1.0f + expf(-ldf(g + m * ldg + f))));
+  }
+}
+
+// x = cap * tanh(x / cap) in place
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) x[e] = cap * tanhf(x[e] / cap);
+}
+
 // The residual update of designs that norm a sublayer's OUTPUT and gate it first, and that hand on a weighted mix of all
 // earlier layers' results instead of the last one:
 //   g     = y * sigmoid(r + rb)                       (r null: g = y; y null: nothing is added)
@@ -520,6 +605,86 @@ extern "C" int lia_argmax_f32(const float* logits, int64_t* next, int B, int V, 
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LIA_CHECK_ARG(logits && next && B > 0 && V > 0, "lia_argmax_f32: bad arguments");
   argmax_f32_kernel<<<B, 256, 0, stream>>>(logits, next, V, suppress_id);
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+extern "C" int lia_embed_scale_pos(const int64_t* ids, const void* table, const void* pos_table, int table_f32, float scale, const int* meta,
+                                   float* x, void* cat, int cat_f32, int rows, int W, int vocab, int max_pos, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(ids && table && meta && x && rows > 0 && W > 0 && vocab > 0 && (!pos_table || max_pos > 0), "lia_embed_scale_pos: bad arguments");
+#define LIA_ESP(T, TC) embed_scale_pos_kernel<T, TC><<<rows, 256, 0, stream>>>(ids, reinterpret_cast<const T*>(table), scale, reinterpret_cast<const T*>(pos_table), meta, x, reinterpret_cast<TC*>(cat), W, vocab, max_pos)
+  if (table_f32 && cat_f32) LIA_ESP(float, float);
+  else if (table_f32) LIA_ESP(float, bf16);
+  else if (cat_f32) LIA_ESP(bf16, float);
+  else LIA_ESP(bf16, bf16);
+#undef LIA_ESP
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+extern "C" int lia_residual_norm(float* x, const void* y, int y_f32, int replace, const float* bias, const float* w, void* h, int h_f32,
+                                 long long ldh, int rows, int W, float eps, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(x && (y || bias || h), "lia_residual_norm: nothing to do");
+  LIA_CHECK_ARG(!replace || y, "lia_residual_norm: replacing the stream needs what replaces it");
+  LIA_CHECK_ARG(rows > 0 && W > 0 && (size_t)W * 4 <= 160 * 1024 && (!h || ldh >= W), "lia_residual_norm: bad shape rows=%d W=%d", rows, W);
+  const size_t smem = (size_t)W * sizeof(float);
+#define LIA_RN(TY, TH)                                                                                                       \
+  do {                                                                                                                       \
+    if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(residual_norm_kernel<TY, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    residual_norm_kernel<TY, TH><<<rows, 256, smem, stream>>>(x, reinterpret_cast<const TY*>(y), replace, bias, w, reinterpret_cast<TH*>(h), ldh, W, eps); \
+  } while (0)
+  if (y_f32 && h_f32) LIA_RN(float, float);
+  else if (y_f32) LIA_RN(float, bf16);
+  else if (h_f32) LIA_RN(bf16, float);
+  else LIA_RN(bf16, bf16);
+#undef LIA_RN
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+extern "C" int lia_rms_norm_rows(const void* in, int in_f32, long long ld, const float* w, void* out, int out_f32, int M, int N, float eps,
+                                 lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(in && w && out && M > 0 && N > 0 && ld >= N, "lia_rms_norm_rows: bad arguments");
+  const unsigned grid = (unsigned)((M + 3) / 4);
+#define LIA_RNR(TI, TO) rms_norm_rows_kernel<TI, TO><<<grid, 128, 0, stream>>>(reinterpret_cast<const TI*>(in), ld, w, reinterpret_cast<TO*>(out), M, N, eps)
+  if (in_f32 && out_f32) LIA_RNR(float, float);
+  else if (in_f32) LIA_RNR(float, bf16);
+  else if (out_f32) LIA_RNR(bf16, float);
+  else LIA_RNR(bf16, bf16);
+#undef LIA_RNR
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+extern "C" int lia_sigmoid_mul(const void* a, int a_f32, long long lda, const void* gate, int gate_f32, long long ldg, void* out, int out_f32,
+                               int M, int F, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(a && gate && out && M > 0 && F > 0 && lda >= F && ldg >= F, "lia_sigmoid_mul: bad arguments");
+  LIA_CHECK_ARG(gate_f32 == out_f32, "lia_sigmoid_mul: the gate and the output have the activations' type");
+  const size_t n = (size_t)M * F;
+  size_t blocks = (n + 255) / 256;
+  const size_t capb = (size_t)lia_sm_count() * 16;
+  if (blocks > capb) blocks = capb;
+#define LIA_SM(TA, TG) sigmoid_mul_kernel<TA, TG, TG><<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const TA*>(a), lda, reinterpret_cast<const TG*>(gate), ldg, reinterpret_cast<TG*>(out), M, F)
+  if (a_f32 && gate_f32) LIA_SM(float, float);
+  else if (a_f32) LIA_SM(float, bf16);
+  else if (gate_f32) LIA_SM(bf16, float);
+  else LIA_SM(bf16, bf16);
+#undef LIA_SM
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
+}
+
+extern "C" int lia_softcap_f32(float* x, long long n, float cap, lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(x && n > 0 && cap > 0.f, "lia_softcap_f32: bad arguments");
+  size_t blocks = ((size_t)n + 255) / 256;
+  const size_t capb = (size_t)lia_sm_count() * 16;
+  if (blocks > capb) blocks = capb;
+  softcap_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, (size_t)n, cap);
   LIA_LAUNCH_CHECK();
   return LIA_OK;
 }

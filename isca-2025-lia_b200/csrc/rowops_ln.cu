@@ -119,6 +119,17 @@ __device__ __forceinline__ float act_apply(float z, int act) {
   }
 }
 
+// the product of a gated feed-forward: act(g) * u, or (LIA_ACT_CLAMPED_SWISH, p0 = limit, p1 = alpha) with g' = min(g, limit) and
+// u' = clamp(u, -limit, limit): g' * sigmoid(alpha g') * (u' + 1)
+__device__ __forceinline__ float gated_apply(float g, float u, int act, float p0, float p1) {
+  if (act == LIA_ACT_CLAMPED_SWISH) {
+    g = fminf(g, p0);
+    u = fminf(fmaxf(u, -p0), p0);
+    return g / (1.0f + expf(-p1 * g)) * (u + 1.0f);
+  }
+  return act_apply(g, act) * u;
+}
+
 // out[m][f] = act(in[m][f]) * in[m][up_off + f]   (up_off < 0: no second factor)
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ in, int ld, int up_off, T* __restrict__ out, int M, int F, int act) {
@@ -233,7 +244,7 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
 template <typename TA, typename TW, typename TC, bool UP, bool GATED>
 __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ Wt, long long sW, TC* __restrict__ C,
                                                        int ldc, const int* __restrict__ perm, const int* __restrict__ tile_expert,
-                                                       const float* __restrict__ wt, int top, int N, int K, int act, int n_real) {
+                                                       const float* __restrict__ wt, int top, int N, int K, int act, int n_real, float p0, float p1) {
   const int e = tile_expert[blockIdx.y];
   if (e < 0 || e >= n_real) return;
   __shared__ float As[16][TM + 4];
@@ -295,7 +306,7 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A,
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
       if (n >= N) continue;
-      if (UP) stf(C + (size_t)(row0 + r) * ldc + n, GATED ? act_apply(acc[i][j], act) * accu[i][j] : act_apply(acc[i][j], act));
+      if (UP) stf(C + (size_t)(row0 + r) * ldc + n, GATED ? gated_apply(acc[i][j], accu[i][j], act, p0, p1) : act_apply(acc[i][j], act));
       else stf(C + (size_t)p * ldc + n, acc[i][j] * wt[p]);
     }
   }
@@ -327,7 +338,7 @@ __device__ __forceinline__ void load8(const float* p, int k, int K, bool vec, fl
 template <typename TA, typename TW, typename TC, bool UP>
 __global__ void __launch_bounds__(128) moe_fewrows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ Wt, long long sW, TC* __restrict__ C,
                                                           int ldc, const int* __restrict__ idx, const float* __restrict__ wt, int top, int N, int K,
-                                                          int act, int gated, int n_real) {
+                                                          int act, int gated, int n_real, float p0, float p1) {
   const int p = blockIdx.y, n = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (n >= N || idx[p] >= n_real) return;
   const TW* wr = Wt + (size_t)idx[p] * sW + (size_t)n * K;
@@ -349,7 +360,7 @@ __global__ void __launch_bounds__(128) moe_fewrows_kernel(const TA* __restrict__
   }
   acc = warp_sum(acc);
   if (UP && gated) accu = warp_sum(accu);
-  if (lane == 0) stf(C + (size_t)p * ldc + n, UP ? (gated ? act_apply(acc, act) * accu : act_apply(acc, act)) : acc * wt[p]);
+  if (lane == 0) stf(C + (size_t)p * ldc + n, UP ? (gated ? gated_apply(acc, accu, act, p0, p1) : act_apply(acc, act)) : acc * wt[p]);
 }
 
 // dst[place] = src[perm[place] / top] for every place of the plan, zeros in the padding: the experts' inputs, expert by expert
@@ -492,6 +503,15 @@ extern "C" int lia_moe_gemm(const void* A, int a_f32, int lda, const void* W, in
 extern "C" int lia_moe_gemm_ext(const void* A, int a_f32, int lda, const void* W, int w_f32, long long w_expert_stride, void* C, int c_f32, int ldc,
                                 const int* perm, const int* tile_expert, int n_tiles, const int* idx, const float* wt, int pairs, int top, int N,
                                 int K, int up, int act, int gated, int n_real, lia_stream_t stream_) {
+  return lia_moe_gemm_act(A, a_f32, lda, W, w_f32, w_expert_stride, C, c_f32, ldc, perm, tile_expert, n_tiles, idx, wt, pairs, top, N, K, up, act, gated,
+                          n_real, 0.f, 0.f, stream_);
+}
+
+// act_p0, act_p1: the activation's parameters (LIA_ACT_CLAMPED_SWISH: limit, alpha; it needs the gated form)
+extern "C" int lia_moe_gemm_act(const void* A, int a_f32, int lda, const void* W, int w_f32, long long w_expert_stride, void* C, int c_f32, int ldc,
+                                const int* perm, const int* tile_expert, int n_tiles, const int* idx, const float* wt, int pairs, int top, int N,
+                                int K, int up, int act, int gated, int n_real, float p0, float p1, lia_stream_t stream_) {
+  LIA_CHECK_ARG(act != LIA_ACT_CLAMPED_SWISH || (gated && p0 > 0.f), "lia_moe_gemm: the clamped activation needs the gated form and a positive limit");
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LIA_CHECK_ARG(A && W && C && idx && wt && pairs > 0 && top > 0 && N > 0 && K > 0 && lda >= K && ldc >= N, "lia_moe_gemm: bad arguments");
   LIA_CHECK_ARG(!gated || up, "lia_moe_gemm: only the up projection can be gated");
@@ -501,18 +521,18 @@ extern "C" int lia_moe_gemm_ext(const void* A, int a_f32, int lda, const void* W
     LIA_CHECK_ARG(pairs <= 65535, "lia_moe_gemm: too many pairs for the few-rows form");
     dim3 grid((N + 3) / 4, pairs);
     if (a_f32) {
-      if (up) moe_fewrows_kernel<float, float, float, true><<<grid, 128, 0, stream>>>((const float*)A, lda, (const float*)W, w_expert_stride, (float*)C, ldc, idx, wt, top, N, K, act, gated, n_real);
-      else moe_fewrows_kernel<float, float, float, false><<<grid, 128, 0, stream>>>((const float*)A, lda, (const float*)W, w_expert_stride, (float*)C, ldc, idx, wt, top, N, K, act, gated, n_real);
+      if (up) moe_fewrows_kernel<float, float, float, true><<<grid, 128, 0, stream>>>((const float*)A, lda, (const float*)W, w_expert_stride, (float*)C, ldc, idx, wt, top, N, K, act, gated, n_real, p0, p1);
+      else moe_fewrows_kernel<float, float, float, false><<<grid, 128, 0, stream>>>((const float*)A, lda, (const float*)W, w_expert_stride, (float*)C, ldc, idx, wt, top, N, K, act, gated, n_real, p0, p1);
     } else {
-      if (up) moe_fewrows_kernel<bf16, bf16, bf16, true><<<grid, 128, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, w_expert_stride, (bf16*)C, ldc, idx, wt, top, N, K, act, gated, n_real);
-      else moe_fewrows_kernel<bf16, bf16, float, false><<<grid, 128, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, w_expert_stride, (float*)C, ldc, idx, wt, top, N, K, act, gated, n_real);
+      if (up) moe_fewrows_kernel<bf16, bf16, bf16, true><<<grid, 128, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, w_expert_stride, (bf16*)C, ldc, idx, wt, top, N, K, act, gated, n_real, p0, p1);
+      else moe_fewrows_kernel<bf16, bf16, float, false><<<grid, 128, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, w_expert_stride, (float*)C, ldc, idx, wt, top, N, K, act, gated, n_real, p0, p1);
     }
     LIA_LAUNCH_CHECK();
     return LIA_OK;
   }
   LIA_CHECK_ARG(tile_expert && n_tiles > 0 && n_tiles <= 65535, "lia_moe_gemm: bad tile plan");
   dim3 grid((N + 63) / 64, n_tiles);
-#define LIA_MG(TA, TC, UP_, GATED_) moe_gemm_kernel<TA, TA, TC, UP_, GATED_><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TA*)W, w_expert_stride, (TC*)C, ldc, perm, tile_expert, wt, top, N, K, act, n_real)
+#define LIA_MG(TA, TC, UP_, GATED_) moe_gemm_kernel<TA, TA, TC, UP_, GATED_><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TA*)W, w_expert_stride, (TC*)C, ldc, perm, tile_expert, wt, top, N, K, act, n_real, p0, p1)
   if (a_f32) {
     if (up && gated) LIA_MG(float, float, true, true);
     else if (up) LIA_MG(float, float, true, false);

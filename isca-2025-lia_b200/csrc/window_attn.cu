@@ -69,6 +69,7 @@ struct PrepArgs {
   int rot_dims, rot_halves;      // channels (2i, 2i+1), i < rot_dims/2, of every head turn by pos * freq[i]; rot_halves != 0: pairs (i, i + rot_dims/2)
   int vmix_mode;                 // 0 none; 1 publish v into v_first; 2 v += lambda (v_first - v)
   float eps, temp_coef, rot_mag, lambda;
+  int Gv = 0;                    // value heads (0: as many as key heads)
 };
 
 // Block per token row; meta[row] = {slot, position}; rows of one portion are consecutive and so are their positions.
@@ -84,7 +85,7 @@ __global__ void __launch_bounds__(256) qkv_prep_kernel(const T* __restrict__ y, 
   __shared__ float red[8];
   const int row = blockIdx.x;
   const int slot = meta[2 * row], pos = meta[2 * row + 1];
-  const int nq = a.H * a.dim, nk = a.G * a.dim, nv = a.G * a.vdim, C = nq + nk + nv;
+  const int nq = a.H * a.dim, nk = a.G * a.dim, nv = (a.Gv > 0 ? a.Gv : a.G) * a.vdim, C = nq + nk + nv;
   float* cs = ch + C;
   const int npair = a.rot_dims / 2;
   for (int i = threadIdx.x; i < npair; i += 256) {
@@ -181,7 +182,24 @@ struct WindowArgs {
   int HB, NG, QR, nsplit;      // query heads per block (spanning at most NG key/value heads), rows per block, key ranges per row
   float scale, softcap;
   int q_f32, gate_mode, ldg;   // queries in fp32; gate: 0 none, 1 fp32 [M][H] as is, 2 sigmoid of the activations' type [M][ldg], per channel
+  int chunk = 0;               // > 0: a position sees only the keys of its own block of `chunk` positions (counted from the sequence's start)
+  int v_div = 1;               // key head g reads value head g / v_div (the value cache holds G / v_div heads)
+  int out_f32 = 0;             // the output in fp32 whatever the caches hold
 };
+
+// first position a query at `pos` sees: the window's start, and the start of its chunk if the mask is chunked
+__device__ __forceinline__ int first_key(const WindowArgs& a, int pos) {
+  int lo = max(0, pos - a.window + 1);
+  if (a.chunk > 0) lo = max(lo, pos - pos % a.chunk);
+  return lo;
+}
+
+// the output in the caches' type or, `out_f32`, in fp32
+template <typename T>
+__device__ __forceinline__ void store_out(T* out, size_t at, float v, const WindowArgs& a) {
+  if (a.out_f32) reinterpret_cast<float*>(out)[at] = v;
+  else stf(out + at, v);
+}
 
 // what the scores and the output take besides q, k, v (each may be null)
 struct WindowExtras {
@@ -258,6 +276,7 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const void* __r
   const int h0 = blockIdx.y * a.HB, z = blockIdx.z;
   const int nh = min(a.HB, a.H - h0), rep = a.H / a.G;
   const int g_lo = h0 / rep, ng = (h0 + nh - 1) / rep - g_lo + 1;
+  const int gv_lo = g_lo / a.v_div, ngv = (g_lo + ng - 1) / a.v_div - gv_lo + 1;      // the value heads behind those key heads
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int VEC = Vec<T>::N;
   const bool aligned = reinterpret_cast<uintptr_t>(kcache) % 16 == 0 && reinterpret_cast<uintptr_t>(vcache) % 16 == 0 &&
@@ -289,14 +308,14 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const void* __r
 #pragma unroll
       for (int i = 0; i < VR; ++i) acc[s][i] = 0.f;
     }
-    const int jb = max(0, pos_first - a.window + 1);
+    const int jb = first_key(a, pos_first);                 // the first key any row of the run sees (first_key grows with pos)
     const int ntiles = (pos_last - jb) / TK + 1, per = (ntiles + a.nsplit - 1) / a.nsplit;
     const int t_end = min(ntiles, (z + 1) * per);
     for (int t = z * per; t < t_end; ++t) {
       const int j0 = jb + t * TK, nk = min(TK, pos_last + 1 - j0);
       __syncthreads();                                        // previous stage fully consumed (and qs written, first time)
       stage_rows(kc, a.G, a.dim, g_lo, ng, j0, nk, ks, DKS, vec_k);
-      stage_rows(vc, a.G, a.vdim, g_lo, ng, j0, nk, vs, a.vdim, vec_v);
+      stage_rows(vc, a.G / a.v_div, a.vdim, gv_lo, ngv, j0, nk, vs, a.vdim, vec_v);
       __syncthreads();
       if (same_head) {
         // All pairs of this warp are rows of ONE query head (nh divides the warp count): a staged key or value row is read
@@ -309,7 +328,7 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const void* __r
 #pragma unroll
         for (int s = 0; s < PP; ++s) {
           const int p = warp + NWARP * s;
-          const int pos = pos_first + p / nh, lo = max(0, pos - a.window + 1);
+          const int pos = pos_first + p / nh, lo = first_key(a, pos);
           active[s] = p < npairs && j0 <= pos && j0 + nk - 1 >= lo;
           if (active[s]) {
             lo_min = min(lo_min, lo);
@@ -343,7 +362,7 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const void* __r
           for (int s = 0; s < PP; ++s) {
             pr[s] = 0.f;
             if (!active[s]) continue;                         // warp-uniform
-            const int pos = pos_first + (warp + NWARP * s) / nh, lo = max(0, pos - a.window + 1);
+            const int pos = pos_first + (warp + NWARP * s) / nh, lo = first_key(a, pos);
             float sc = dot[s] * sc_mul;
             if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
             const int j = j0 + lane;
@@ -357,7 +376,7 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const void* __r
 #pragma unroll
             for (int c = 0; c < VR; ++c) acc[s][c] *= al;
           }
-          const float* vr = vs + gi * TK * a.vdim;
+          const float* vr = vs + ((gi + g_lo) / a.v_div - gv_lo) * TK * a.vdim;
           const int jj_end = min(nk - 1, pos_max - j0);
           for (int jj = max(0, lo_min - j0); jj <= jj_end; ++jj) {
             float vv[VR];
@@ -381,7 +400,7 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const void* __r
         const int p = warp + NWARP * s;
         if (p >= npairs) continue;
         const int i = p / nh, hh = p - i * nh;
-        const int pos = pos_first + i, lo = max(0, pos - a.window + 1);
+        const int pos = pos_first + i, lo = first_key(a, pos);
         if (j0 > pos || j0 + nk - 1 < lo) continue;          // no key of this stage is visible to the row (warp-uniform)
         const int h = h0 + hh, gi = h / rep - g_lo;
         const float* kr = ks + (gi * TK + lane) * DKS;
@@ -409,7 +428,7 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const void* __r
         m_run[s] = m_new;
 #pragma unroll
         for (int c = 0; c < VR; ++c) acc[s][c] *= al;
-        const float* vr = vs + gi * TK * a.vdim;
+        const float* vr = vs + ((gi + g_lo) / a.v_div - gv_lo) * TK * a.vdim;
         const int jj_end = min(nk - 1, pos - j0);
         for (int jj = max(0, lo - j0); jj <= jj_end; ++jj) {
           const float pw = __shfl_sync(0xffffffffu, pr, jj);
@@ -432,7 +451,7 @@ __global__ void __launch_bounds__(NWARP * 32) window_attn_kernel(const void* __r
 #pragma unroll
         for (int c = 0; c < VR; ++c) {
           const int ch = lane + 32 * c;
-          if (ch < a.vdim) stf(out + rh * a.vdim + ch, acc[s][c] * invl * gate_of<T>(x, a, (size_t)(r + i), h0 + hh, ch));
+          if (ch < a.vdim) store_out(out, rh * a.vdim + ch, acc[s][c] * invl * gate_of<T>(x, a, (size_t)(r + i), h0 + hh, ch), a);
         }
       } else {
 #pragma unroll
@@ -469,8 +488,31 @@ __global__ void __launch_bounds__(128) window_combine_kernel(const float* __rest
       const float2 ml = part_ml[rh * nsplit + z];
       if (ml.y > 0.f) s = fmaf(part[(rh * nsplit + z) * vdim + c], expf(ml.x - m), s);
     }
-    stf(out + rh * vdim + c, s * invl * gate_of<T>(x, a, row, h, c));
+    store_out(out, rh * vdim + c, s * invl * gate_of<T>(x, a, row, h, c), a);
   }
+}
+
+// Differential attention's last step.  `a` [M][G][2][rep][vdim] fp32 holds both maps' outputs (the query heads of key/value
+// group g side by side, map 1 then map 2); head h = g * rep + r of the result is
+//     o = a1 - lambda * a2,   out = mult * o / rms(o),   rms taken (with eps under the root) over that head's vdim entries.
+// One warp per (row, head).
+template <typename T>
+__global__ void __launch_bounds__(128) diff_combine_kernel(const float* __restrict__ a, T* __restrict__ out, int M, int H, int G, int vdim,
+                                                           float lambda, float mult, float eps) {
+  const long long pair = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (pair >= (long long)M * H) return;
+  const size_t row = pair / H;
+  const int h = (int)(pair - row * H), rep = H / G, g = h / rep, r = h - g * rep;
+  const float* a1 = a + (row * 2 * H + (size_t)(g * 2) * rep + r) * vdim;
+  const float* a2 = a1 + (size_t)rep * vdim;
+  float ss = 0.f;
+  for (int c = lane; c < vdim; c += 32) {
+    const float o = a1[c] - lambda * a2[c];
+    ss += o * o;
+  }
+  const float inv = mult / sqrtf(warp_sum(ss) / (float)vdim + eps);
+  for (int c = lane; c < vdim; c += 32) stf(out + (row * H + h) * vdim + c, (a1[c] - lambda * a2[c]) * inv);
 }
 
 size_t attn_smem(const WindowArgs& a) {
@@ -530,6 +572,18 @@ extern "C" int lia_qkv_prep(const void* y, int act_f32, int ld, int q_off, int k
                             float temp_coef, int temp_every, const double* freq, int rot_dims, int rot_halves, float rot_mag, int vmix_mode,
                             float lambda, float* v_first, const int* meta, float* q_out, void* kcache, long long k_slot_stride, void* vcache,
                             long long v_slot_stride, int M, int H, int G, int dim, int vdim, lia_stream_t stream_) {
+  return lia_qkv_prep_heads(y, act_f32, ld, q_off, k_off, v_off, bias, wconv, conv_state, taps, norm_mode, qnorm_w, knorm_w, eps, temp_coef, temp_every,
+                            freq, rot_dims, rot_halves, rot_mag, vmix_mode, lambda, v_first, meta, q_out, kcache, k_slot_stride, vcache, v_slot_stride,
+                            M, H, G, G, dim, vdim, stream_);
+}
+
+// Gv value heads beside G key heads (several attention maps over one set of values have G = maps * Gv)
+extern "C" int lia_qkv_prep_heads(const void* y, int act_f32, int ld, int q_off, int k_off, int v_off, const float* bias, const float* wconv,
+                                  const float* conv_state, int taps, int norm_mode, const float* qnorm_w, const float* knorm_w, float eps,
+                                  float temp_coef, int temp_every, const double* freq, int rot_dims, int rot_halves, float rot_mag, int vmix_mode,
+                                  float lambda, float* v_first, const int* meta, float* q_out, void* kcache, long long k_slot_stride, void* vcache,
+                                  long long v_slot_stride, int M, int H, int G, int Gv, int dim, int vdim, lia_stream_t stream_) {
+  LIA_CHECK_ARG(Gv > 0, "lia_qkv_prep: no value heads");
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LIA_CHECK_ARG(y && meta && q_out && kcache && vcache, "lia_qkv_prep: null pointer");
   LIA_CHECK_ARG(M > 0 && H > 0 && G > 0 && dim > 0 && vdim > 0 && taps >= 1 && taps <= 16 && (taps == 1 || (wconv && conv_state)),
@@ -538,8 +592,9 @@ extern "C" int lia_qkv_prep(const void* y, int act_f32, int ld, int q_off, int k
   LIA_CHECK_ARG(rot_dims >= 0 && rot_dims <= dim && rot_dims % 2 == 0 && (rot_dims == 0 || freq), "lia_qkv_prep: cannot rotate %d of %d channels", rot_dims, dim);
   LIA_CHECK_ARG(vmix_mode >= 0 && vmix_mode <= 2 && (vmix_mode == 0 || v_first), "lia_qkv_prep: bad value-mixing mode %d", vmix_mode);
   PrepArgs a{H, G, dim, vdim, q_off, k_off, v_off, taps, norm_mode, temp_every, rot_dims, rot_halves, vmix_mode, eps, temp_coef, rot_mag, lambda};
-  const size_t smem = ((size_t)(H + G) * dim + (size_t)G * vdim + rot_dims) * sizeof(float);
-  LIA_CHECK_ARG(smem <= 160 * 1024, "lia_qkv_prep: %d channels do not fit shared memory", (H + G) * dim + G * vdim);
+  a.Gv = Gv;
+  const size_t smem = ((size_t)(H + G) * dim + (size_t)Gv * vdim + rot_dims) * sizeof(float);
+  LIA_CHECK_ARG(smem <= 160 * 1024, "lia_qkv_prep: %d channels do not fit shared memory", (H + G) * dim + Gv * vdim);
   if (act_f32) {
     if (smem > 48 * 1024) LIA_CUDA(cudaFuncSetAttribute(qkv_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     qkv_prep_kernel<float><<<M, 256, smem, stream>>>(reinterpret_cast<const float*>(y), ld, bias, wconv, conv_state, qnorm_w, knorm_w, freq, meta, v_first,
@@ -571,6 +626,17 @@ extern "C" int lia_window_attn_ext(const void* q, int ldq, int q_f32, int act_f3
                                    const void* gate, int gate_mode, int ldg, void* out, float* workspace, int M, int H, int G, int dim, int vdim,
                                    int window, float scale, float softcap, int heads_per_block, int rows_per_block, int nsplit,
                                    lia_stream_t stream_) {
+  return lia_window_attn_masked(q, ldq, q_f32, act_f32, kcache, k_slot_stride, vcache, v_slot_stride, meta, temp, slopes, sink, gate, gate_mode, ldg, out,
+                                0, workspace, M, H, G, 1, dim, vdim, window, 0, scale, softcap, heads_per_block, rows_per_block, nsplit, stream_);
+}
+
+// chunk > 0: the chunked mask; v_div: key heads per value head; out_f32: fp32 output on caches of any type
+extern "C" int lia_window_attn_masked(const void* q, int ldq, int q_f32, int act_f32, const void* kcache, long long k_slot_stride, const void* vcache,
+                                      long long v_slot_stride, const int* meta, const float* temp, const float* slopes, const float* sink,
+                                      const void* gate, int gate_mode, int ldg, void* out, int out_f32, float* workspace, int M, int H, int G,
+                                      int v_div, int dim, int vdim, int window, int chunk, float scale, float softcap, int heads_per_block,
+                                      int rows_per_block, int nsplit, lia_stream_t stream_) {
+  LIA_CHECK_ARG(v_div >= 1 && G % v_div == 0 && chunk >= 0, "lia_window_attn: %d key heads do not share value heads in groups of %d (chunk %d)", G, v_div, chunk);
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   LIA_CHECK_ARG(q && kcache && vcache && meta && out, "lia_window_attn: null pointer");
   LIA_CHECK_ARG(M > 0 && H > 0 && G > 0 && H % G == 0 && dim > 0 && vdim > 0 && vdim <= 512 && H <= 65535 && ldq >= H * dim,
@@ -582,6 +648,9 @@ extern "C" int lia_window_attn_ext(const void* q, int ldq, int q_f32, int act_f3
   LIA_CHECK_ARG(HB >= 1 && HB <= NWARP && (HB % rep == 0 || rep % HB == 0), "lia_window_attn: %d heads per block do not fit groups of %d", HB, rep);
   LIA_CHECK_ARG(rows_per_block >= 1 && nsplit >= 1 && nsplit <= 64 && (nsplit == 1 || workspace), "lia_window_attn: bad rows per block (%d) or key ranges (%d)", rows_per_block, nsplit);
   WindowArgs a{H, G, dim, vdim, window, HB, HB >= rep ? HB / rep : 1, rows_per_block, nsplit, scale, softcap, q_f32 || act_f32, gate_mode, ldg};
+  a.chunk = chunk;
+  a.v_div = v_div;
+  a.out_f32 = out_f32 || act_f32;
   LIA_CHECK_ARG(attn_smem(a) <= 200 * 1024, "lia_window_attn: heads of %d + %d numbers do not fit the shared-memory stage", dim, vdim);
   const WindowExtras x{temp, slopes, sink, gate};
   if (act_f32) return dispatch_attn<float>(q, ldq, kcache, k_slot_stride, vcache, v_slot_stride, meta, x, out, workspace, M, a, stream);
@@ -595,4 +664,15 @@ extern "C" int lia_window_attn(const void* q, int ldq, int act_f32, const void* 
   LIA_CHECK_ARG(temp && window > 0, "lia_window_attn: needs a temperature per head and a positive window");
   return lia_window_attn_ext(q, ldq, act_f32, act_f32, kcache, k_slot_stride, vcache, v_slot_stride, meta, temp, nullptr, nullptr, nullptr, 0, 0, out,
                              workspace, M, H, G, dim, vdim, window, scale, softcap, heads_per_block, rows_per_block, nsplit, stream_);
+}
+
+extern "C" int lia_diff_combine(const float* a, void* out, int act_f32, int M, int H, int G, int vdim, float lambda, float mult, float eps,
+                                lia_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  LIA_CHECK_ARG(a && out && M > 0 && H > 0 && G > 0 && H % G == 0 && vdim > 0, "lia_diff_combine: bad arguments");
+  const unsigned grid = (unsigned)(((long long)M * H + 3) / 4);
+  if (act_f32) diff_combine_kernel<float><<<grid, 128, 0, stream>>>(a, reinterpret_cast<float*>(out), M, H, G, vdim, lambda, mult, eps);
+  else diff_combine_kernel<bf16><<<grid, 128, 0, stream>>>(a, reinterpret_cast<bf16*>(out), M, H, G, vdim, lambda, mult, eps);
+  LIA_LAUNCH_CHECK();
+  return LIA_OK;
 }

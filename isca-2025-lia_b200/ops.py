@@ -410,11 +410,11 @@ def mlstm_scan(q, k, v, gates, state_S, state_n, state_m, segs, H, dim, vdim, q_
 
 
 def headnorm_gate(o, w, gate, out, H, vdim, eps, gate_silu=False):
-    """out = o / rms_per_head(o) * w * sigmoid(gate) (``gate_silu``: * silu(gate))."""
+    """out = o / rms_per_head(o) * w * sigmoid(gate) (``gate_silu``: * silu(gate); ``gate`` None: the norm alone)."""
     _req(o, "o", F32); _req(w, "w", F32)
-    ldg = _rowmajor(gate, "gate")
+    ldg = _rowmajor(gate, "gate") if gate is not None else 0
     M = o.shape[0]
-    if not out.is_contiguous() or tuple(out.shape) != (M, H * vdim) or out.dtype != gate.dtype:
+    if not out.is_contiguous() or tuple(out.shape) != (M, H * vdim) or (gate is not None and out.dtype != gate.dtype):
         raise _lib.LiaError("headnorm_gate: out must be a contiguous [M, H*vdim] tensor of the gate's dtype")
     check(_lib.load().lia_headnorm_gate(_p(o), _p(w), _p(gate), ldg, _p(out), _f32(out), M, H, vdim, float(eps), int(gate_silu), _stream()),
           "lia_headnorm_gate")
@@ -422,15 +422,22 @@ def headnorm_gate(o, w, gate, out, H, vdim, eps, gate_silu=False):
     return out
 
 
-def latent_prep(q, dkv, c_norm_w, inv_freq, meta, cache, qa, H, dim, rot, rot_dims, kv_rank, eps):
-    """Normalised latent + rotated shared key part into ``cache[slot, pos]``; rotated query parts into ``qa[..., kv_rank:]``."""
+def latent_prep(q, dkv, c_norm_w, inv_freq, meta, cache, qa, H, dim, rot, rot_dims, kv_rank, eps, pairs=False, rot_mag=1.0):
+    """Normalised latent + rotated shared key part into ``cache[slot, pos]``; rotated query parts into ``qa[..., kv_rank:]``.
+    ``pairs``: channels (2i, 2i+1) turn together by angles from a float64 frequency table, cos and sin times ``rot_mag``;
+    otherwise channel i turns with i + rot_dims/2 by fp32 angles."""
     ldq, ldd = _rowmajor(q, "q"), _rowmajor(dkv, "dkv")
-    _req(c_norm_w, "c_norm_w", F32); _req(inv_freq, "inv_freq", F32); _req(meta, "meta", torch.int32); _req(qa, "qa", F32)
+    _req(c_norm_w, "c_norm_w", F32); _req(meta, "meta", torch.int32); _req(qa, "qa", F32)
+    _req(inv_freq, "inv_freq", torch.float64 if pairs else F32)
     M = q.shape[0]
-    if cache.dtype != q.dtype or dkv.dtype != q.dtype or not cache.is_contiguous() or cache.shape[2] != kv_rank + rot:
-        raise _lib.LiaError("latent_prep: cache must be a contiguous [slots, capacity, kv_rank + rot] tensor of the activations' dtype")
-    check(_lib.load().lia_latent_prep(_p(q), ldq, _p(dkv), ldd, _f32(q), _p(c_norm_w), _p(inv_freq), _p(meta), _p(cache), cache.stride(0),
-                                      _p(qa), M, H, dim, rot, rot_dims, kv_rank, float(eps), _stream()), "lia_latent_prep")
+    if cache.dtype != q.dtype or dkv.dtype != q.dtype or not cache.is_contiguous() or cache.shape[2] != kv_rank + rot or inv_freq.numel() != rot_dims // 2:
+        raise _lib.LiaError("latent_prep: cache must be a contiguous [slots, capacity, kv_rank + rot] tensor of the activations' dtype, rot_dims / 2 frequencies")
+    if pairs:
+        check(_lib.load().lia_latent_prep_pairs(_p(q), ldq, _p(dkv), ldd, _f32(q), _p(c_norm_w), _p(inv_freq), float(rot_mag), _p(meta), _p(cache),
+                                                cache.stride(0), _p(qa), M, H, dim, rot, rot_dims, kv_rank, float(eps), _stream()), "lia_latent_prep_pairs")
+    else:
+        check(_lib.load().lia_latent_prep(_p(q), ldq, _p(dkv), ldd, _f32(q), _p(c_norm_w), _p(inv_freq), _p(meta), _p(cache), cache.stride(0),
+                                          _p(qa), M, H, dim, rot, rot_dims, kv_rank, float(eps), _stream()), "lia_latent_prep")
     count_launches()
 
 
@@ -470,7 +477,7 @@ def latent_attn(qa, cache, meta, gate, out, H, kv_rank, rot, scale, max_ctx=0):
 # Models whose sublayers sit between layer norms on a 32-bit residual stream: decay / delta-rule recurrences, sliding-window
 # attention with grouped key/value heads, dense and mixture-of-experts feed-forwards.  (Not in the reference either.)
 # ------------------------------------------------------------------------------------------------------------------
-ACT_NONE, ACT_RELU, ACT_SILU, ACT_GELU_ERF, ACT_GELU_TANH = 0, 1, 2, 3, 4
+ACT_NONE, ACT_RELU, ACT_SILU, ACT_GELU_ERF, ACT_GELU_TANH, ACT_CLAMPED_SWISH = 0, 1, 2, 3, 4, 5
 I32 = torch.int32
 
 
@@ -555,20 +562,21 @@ def moe_plan(idx, E, perm, tile_expert, pos_of):
     count_launches()
 
 
-def moe_gemm(a, w, out, idx, wt, top, up, act=ACT_NONE, perm=None, tile_expert=None, gated=False):
+def moe_gemm(a, w, out, idx, wt, top, up, act=ACT_NONE, perm=None, tile_expert=None, gated=False, act_params=(0.0, 0.0)):
     """One projection of every expert over its own rows; ``w`` [E, N, K].  up: out[place] = act(a[token] @ w[e].T);
     down: out[pair] = wt[pair] * a[place] @ w[e].T (fp32).  Without a plan (``perm`` None) a pair's place is the pair.
     ``gated`` (up only): ``w`` is [E, 2N, K], N gate rows then N up rows, and out = act(gate) * up.  Pairs whose expert
-    index is E or more (experts without weights) are left out."""
+    index is E or more (experts without weights) are left out.  ``act_params``: (limit, alpha) of ACT_CLAMPED_SWISH, the gated
+    activation g' sigmoid(alpha g') (u' + 1) on g' = min(g, limit), u' = clamp(u, -limit, limit)."""
     _dev(a, "a"); _dev(w, "w"); _dev(out, "out")
     E, N, K = w.shape
     if gated:
         N //= 2
     if not (w.is_contiguous() and a.is_contiguous() and out.is_contiguous() and a.shape[1] == K and out.shape[1] == N):
         raise _lib.LiaError(f"moe_gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    check(_lib.load().lia_moe_gemm_ext(_p(a), _f32(a), K, _p(w), _f32(w), w.stride(0), _p(out), _f32(out), N, _p(perm), _p(tile_expert),
+    check(_lib.load().lia_moe_gemm_act(_p(a), _f32(a), K, _p(w), _f32(w), w.stride(0), _p(out), _f32(out), N, _p(perm), _p(tile_expert),
                                        tile_expert.numel() if tile_expert is not None else 0, _p(idx), _p(wt), idx.numel(), top, N, K, int(up), act,
-                                       int(gated), E, _stream()), "lia_moe_gemm")
+                                       int(gated), E, float(act_params[0]), float(act_params[1]), _stream()), "lia_moe_gemm")
     count_launches()
     return out
 
@@ -712,21 +720,26 @@ def window_attn_plan(M, nseg, H, G, dim, vdim, window, max_ctx, sms):
 
 
 def window_attn(q, kcache, vcache, meta, temp, out, H, G, dim, vdim, window, scale, softcap, nseg=None, max_ctx=0, slopes=None, sink=None,
-                gate=None, gate_per_head=False):
+                gate=None, gate_per_head=False, chunk=0, v_div=1):
     """Softmax attention of every row over the last ``window`` cached positions of its sequence (csrc/window_attn.cu);
     ``window`` <= 0: over its whole history.  ``nseg``: portions in the step (None: one row each); ``max_ctx``: an upper
     bound of the rows' history lengths (0: unknown, no split of the keys).  ``temp`` [H] multiplies the scores, ``slopes``
     [H] take slope * distance off them, ``sink`` [H] joins the denominator; ``gate`` multiplies the output: fp32 [M, H]
     as it is (``gate_per_head``), else sigmoid of a pre-activation per channel (a column slice of the activations' type).
-    ``q`` may be fp32 while the caches are bf16."""
+    ``q`` may be fp32 while the caches are bf16, and so may ``out``.  ``chunk`` > 0: a position sees only the keys of its own
+    block of ``chunk`` positions (blocks counted from the sequence's start).  ``v_div``: key head g reads value head g // v_div
+    (the value cache holds G // v_div heads: several attention maps over one set of values)."""
     ldq = _rowmajor(q, "q")
     _req(meta, "meta", I32)
     for t, n in ((temp, "temp"), (slopes, "slopes"), (sink, "sink")):
         if t is not None and (_req(t, n, F32).numel() != H):
             raise _lib.LiaError(f"window_attn: {n} must be [H]")
     M = q.shape[0]
-    if not (out.is_contiguous() and tuple(out.shape) == (M, H * vdim) and out.dtype == kcache.dtype == vcache.dtype and q.dtype in (F32, out.dtype)):
-        raise _lib.LiaError("window_attn: out must be a contiguous [M, H * vdim] tensor of the caches' dtype, q of that dtype or fp32")
+    if not (out.is_contiguous() and tuple(out.shape) == (M, H * vdim) and kcache.dtype == vcache.dtype and out.dtype in (F32, kcache.dtype)
+            and q.dtype in (F32, kcache.dtype)):
+        raise _lib.LiaError("window_attn: out must be a contiguous [M, H * vdim] tensor, out and q of the caches' dtype or fp32")
+    if v_div < 1 or G % v_div or chunk < 0:
+        raise _lib.LiaError(f"window_attn: {G} key heads do not share value heads in groups of {v_div} (chunk {chunk})")
     gate_mode, ldg = 0, 0
     if gate is not None:
         ldg = _rowmajor(gate, "gate")
@@ -736,16 +749,17 @@ def window_attn(q, kcache, vcache, meta, temp, out, H, G, dim, vdim, window, sca
                 raise _lib.LiaError("window_attn: a per-head gate must be a contiguous fp32 [M, H] tensor")
         else:
             gate_mode = 2
-            if gate.dtype != out.dtype or tuple(gate.shape) != (M, H * vdim):
+            if gate.dtype != kcache.dtype or tuple(gate.shape) != (M, H * vdim):
                 raise _lib.LiaError("window_attn: a per-channel gate must be an [M, H * vdim] slice of the activations' dtype")
     window = int(window) if window > 0 else 1 << 30
-    hb, qr, nsplit = window_attn_plan(M, nseg if nseg is not None else M, H, G, dim, vdim, window, max_ctx, _sm_count(q.device))
+    span = min(window, int(chunk)) if chunk > 0 else window               # the most keys a row can see
+    hb, qr, nsplit = window_attn_plan(M, nseg if nseg is not None else M, H, G, dim, vdim, span, max_ctx, _sm_count(q.device))
     ws = None
     if nsplit > 1:
         ws = torch.empty(_lib.load().lia_window_attn_workspace_floats(M, H, vdim, nsplit), dtype=F32, device=q.device)
-    check(_lib.load().lia_window_attn_ext(_p(q), ldq, _f32(q), _f32(out), _p(kcache), kcache.stride(0), _p(vcache), vcache.stride(0), _p(meta), _p(temp),
-                                          _p(slopes), _p(sink), _p(gate), gate_mode, ldg, _p(out), _p(ws), M, H, G, dim, vdim, window, float(scale),
-                                          float(softcap), hb, qr, nsplit, _stream()), "lia_window_attn")
+    check(_lib.load().lia_window_attn_masked(_p(q), ldq, _f32(q), _f32(kcache), _p(kcache), kcache.stride(0), _p(vcache), vcache.stride(0), _p(meta),
+                                             _p(temp), _p(slopes), _p(sink), _p(gate), gate_mode, ldg, _p(out), _f32(out), _p(ws), M, H, G, int(v_div),
+                                             dim, vdim, window, int(chunk), float(scale), float(softcap), hb, qr, nsplit, _stream()), "lia_window_attn")
     count_launches(2 if nsplit > 1 else 1)
     return out
 
@@ -760,14 +774,16 @@ VMIX_NONE, VMIX_PUBLISH, VMIX_BLEND = 0, 1, 2
 
 def qkv_prep(y, offs, meta, q_out, kcache, vcache, H, G, dim, vdim, eps, bias=None, wconv=None, conv_state=None, taps=1, norm_mode=NORM_NONE,
              qnorm_w=None, knorm_w=None, temp_coef=0.0, temp_every=0, freq=None, rot_dims=0, rot_halves=False, rot_mag=1.0, vmix_mode=VMIX_NONE,
-             vmix=0.0, v_first=None):
+             vmix=0.0, v_first=None, v_heads=None):
     """The q | k | v columns of ``y`` (column offsets ``offs``) become attention inputs (csrc/window_attn.cu, qkv_prep): bias,
     short causal convolution, RMS norm of q and k, query temperature, rotation of channel pairs, value blend; q into ``q_out``
-    (fp32), k and v into the caches at every row's (slot, position)."""
+    (fp32), k and v into the caches at every row's (slot, position).  ``v_heads``: value heads if they are not as many as
+    the G key heads."""
     ld = _rowmajor(y, "y")
     _req(meta, "meta", I32); _req(q_out, "q_out", F32)
-    M, C = y.shape[0], (H + G) * dim + G * vdim
-    for t, n, shape in ((bias, "bias", (C,)), (wconv, "wconv", (C, taps)), (v_first, "v_first", (M, G * vdim))):
+    Gv = G if v_heads is None else int(v_heads)
+    M, C = y.shape[0], (H + G) * dim + Gv * vdim
+    for t, n, shape in ((bias, "bias", (C,)), (wconv, "wconv", (C, taps)), (v_first, "v_first", (M, Gv * vdim))):
         if t is not None and tuple(_req(t, n, F32).shape) != shape:
             raise _lib.LiaError(f"qkv_prep: {n} must be fp32 {shape}, got {tuple(t.shape)}")
     if taps > 1 and (conv_state is None or tuple(_req(conv_state, "conv_state", F32).shape[1:]) != (taps - 1, C)):
@@ -778,12 +794,12 @@ def qkv_prep(y, offs, meta, q_out, kcache, vcache, H, G, dim, vdim, eps, bias=No
     if rot_dims and (freq is None or freq.dtype != torch.float64 or not freq.is_cuda or freq.numel() != rot_dims // 2):
         raise _lib.LiaError("qkv_prep: the rotation needs rot_dims / 2 frequencies as a CUDA float64 tensor")
     if not (kcache.dtype == vcache.dtype == y.dtype and kcache.is_contiguous() and vcache.is_contiguous() and kcache.shape[2] == G * dim
-            and vcache.shape[2] == G * vdim and tuple(q_out.shape) == (M, H * dim)):
+            and vcache.shape[2] == Gv * vdim and tuple(q_out.shape) == (M, H * dim)):
         raise _lib.LiaError("qkv_prep: caches must be contiguous [slots, capacity, G * dim | G * vdim] tensors of the activations' dtype, q_out [M, H * dim]")
-    check(_lib.load().lia_qkv_prep(_p(y), _f32(y), ld, offs[0], offs[1], offs[2], _p(bias), _p(wconv), _p(conv_state) if taps > 1 else None, int(taps) if wconv is not None else 1,
+    check(_lib.load().lia_qkv_prep_heads(_p(y), _f32(y), ld, offs[0], offs[1], offs[2], _p(bias), _p(wconv), _p(conv_state) if taps > 1 else None, int(taps) if wconv is not None else 1,
                                    norm_mode, _p(qnorm_w), _p(knorm_w), float(eps), float(temp_coef), int(temp_every), _p(freq), int(rot_dims),
                                    int(rot_halves), float(rot_mag), vmix_mode, float(vmix), _p(v_first), _p(meta), _p(q_out), _p(kcache),
-                                   kcache.stride(0), _p(vcache), vcache.stride(0), M, H, G, dim, vdim, _stream()), "lia_qkv_prep")
+                                   kcache.stride(0), _p(vcache), vcache.stride(0), M, H, G, Gv, dim, vdim, _stream()), "lia_qkv_prep")
     count_launches()
 
 
@@ -823,5 +839,119 @@ def poly_norm(inp, F, coef, out, eps):
     if tuple(out.shape) != (M, F) or not out.is_contiguous() or out.dtype != inp.dtype or _req(coef, "coef", F32).numel() != 4:
         raise _lib.LiaError("poly_norm: out must be a contiguous [M, F] tensor of the input's dtype, coef fp32 [4]")
     check(_lib.load().lia_poly_norm(_p(inp), ld, _p(coef), _p(out), _f32(out), M, F, float(eps), _stream()), "lia_poly_norm")
+    count_launches()
+    return out
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# Pre-norm designs with learned positions and per-channel norm weights: latent queries, several attention maps over shared
+# values, the forget-gate recurrence.  (Not in the reference either.)
+# ------------------------------------------------------------------------------------------------------------------
+def embed_scale_pos(ids, table, pos_table, scale, meta, x, cat=None):
+    """x[r] = table[ids[r]] * scale + pos_table[position of row r] in fp32 (``pos_table`` may be None).  ``cat`` [rows, 2 W]
+    (activations' dtype) receives the row twice, side by side."""
+    _req(ids, "ids", torch.int64); _req(x, "x", F32); _req(meta, "meta", I32); _dev(table, "table")
+    rows, W = x.shape
+    if pos_table is not None and (pos_table.dtype != table.dtype or pos_table.shape[1] != W or not pos_table.is_contiguous()):
+        raise _lib.LiaError("embed_scale_pos: the position table must be a contiguous [positions, W] tensor of the token table's dtype")
+    if cat is not None and not (cat.is_cuda and cat.is_contiguous() and tuple(cat.shape) == (rows, 2 * W)):
+        raise _lib.LiaError("embed_scale_pos: cat must be a contiguous [rows, 2 W] tensor")
+    check(_lib.load().lia_embed_scale_pos(_p(ids), _p(table), _p(pos_table), _f32(table), float(scale), _p(meta), _p(x), _p(cat),
+                                          _f32(cat) if cat is not None else 0, rows, W, table.shape[0],
+                                          pos_table.shape[0] if pos_table is not None else 0, _stream()), "lia_embed_scale_pos")
+    count_launches()
+    return x
+
+
+def residual_norm(x, y, w, h, eps, replace=False, bias=None):
+    """x = (0 if ``replace`` else x) + y + bias, then h = w * x / rms(x) (``w`` None: h = x in its dtype).  x is the fp32 residual
+    stream, updated in place; ``y`` [rows, W], ``bias`` fp32 [W] and ``h`` (a row-major view: it may be the left half of a wider
+    buffer) may each be None."""
+    _req(x, "x", F32)
+    rows, W = x.shape
+    if y is not None and not (y.is_cuda and y.is_contiguous() and tuple(y.shape) == (rows, W)):
+        raise _lib.LiaError(f"residual_norm: y must be a contiguous CUDA [{rows}, {W}] tensor")
+    ldh = 0
+    if h is not None:
+        ldh = _rowmajor(h, "h")
+        if tuple(h.shape) != (rows, W):
+            raise _lib.LiaError(f"residual_norm: h must be [{rows}, {W}]")
+    for t, n in ((bias, "bias"), (w, "w")):
+        if t is not None and _req(t, n, F32).numel() != W:
+            raise _lib.LiaError(f"residual_norm: {n} must be fp32 [{W}]")
+    check(_lib.load().lia_residual_norm(_p(x), _p(y), _f32(y) if y is not None else 0, int(replace), _p(bias), _p(w), _p(h),
+                                        _f32(h) if h is not None else 0, ldh, rows, W, float(eps), _stream()), "lia_residual_norm")
+    count_launches()
+    return x
+
+
+def rms_norm_rows(inp, w, out, eps):
+    """out = w * z / rms(z) over the rows z of ``inp`` (a column slice is fine); out contiguous."""
+    ld = _rowmajor(inp, "inp")
+    M, N = inp.shape
+    if not (out.is_cuda and out.is_contiguous() and tuple(out.shape) == (M, N)) or _req(w, "w", F32).numel() != N:
+        raise _lib.LiaError("rms_norm_rows: out must be a contiguous [M, N] tensor, w fp32 [N]")
+    check(_lib.load().lia_rms_norm_rows(_p(inp), _f32(inp), ld, _p(w), _p(out), _f32(out), M, N, float(eps), _stream()), "lia_rms_norm_rows")
+    count_launches()
+    return out
+
+
+def sigmoid_mul(a, gate, out):
+    """out = a * sigmoid(gate), element by element; ``a`` fp32 or the activations' dtype, ``gate`` and ``out`` the activations' dtype."""
+    lda, ldg = _rowmajor(a, "a"), _rowmajor(gate, "gate")
+    M, F = a.shape
+    if tuple(gate.shape) != (M, F) or not (out.is_cuda and out.is_contiguous() and tuple(out.shape) == (M, F) and out.dtype == gate.dtype):
+        raise _lib.LiaError("sigmoid_mul: gate [M, F], out a contiguous [M, F] tensor of the gate's dtype")
+    check(_lib.load().lia_sigmoid_mul(_p(a), _f32(a), lda, _p(gate), _f32(gate), ldg, _p(out), _f32(out), M, F, _stream()), "lia_sigmoid_mul")
+    count_launches()
+    return out
+
+
+def softcap(x, cap):
+    """x = cap * tanh(x / cap) in place (fp32)."""
+    _req(x, "x", F32)
+    check(_lib.load().lia_softcap_f32(_p(x), x.numel(), float(cap), _stream()), "lia_softcap_f32")
+    count_launches()
+    return x
+
+
+def forget_gate_prep(y, offs, f_bias, low, out, nq, nv):
+    """The q | f | v columns of ``y`` (column offsets ``offs``) -> out [M, 2 nq + nv] fp32 = silu(q) | low + (1 - low) sigmoid(f + f_bias) | v."""
+    ld = _rowmajor(y, "y")
+    M = y.shape[0]
+    _req(out, "out", F32)
+    if tuple(out.shape) != (M, 2 * nq + nv) or _req(low, "low", F32).numel() != nq or (f_bias is not None and _req(f_bias, "f_bias", F32).numel() != nq):
+        raise _lib.LiaError("forget_gate_prep: out must be [M, 2 nq + nv], low and f_bias fp32 [nq]")
+    check(_lib.load().lia_forget_gate_prep(_p(y), _f32(y), ld, offs[0], offs[1], offs[2], _p(f_bias), _p(low), _p(out), M, nq, nv, _stream()),
+          "lia_forget_gate_prep")
+    count_launches()
+    return out
+
+
+def forget_scan(q, f, v, state_S, segs, H, dim, vdim, o):
+    """Per head and channel d: S[d] <- f[d] S[d] + (1 - f[d]) v, then o = sum_d q[d] S[d], over every portion of the step (csrc/linear_scan.cu); q, f: fp32 column
+    slices of one buffer, v fp32; state_S [slots, H, vdim, dim]."""
+    ld = _rowmajor(q, "q")
+    if _rowmajor(f, "f") != ld or not (q.dtype == f.dtype == v.dtype == F32):
+        raise _lib.LiaError("forget_scan: q and f must be fp32 slices of one buffer, v fp32")
+    ldv = _rowmajor(v, "v")
+    _req(state_S, "state_S", F32); _req(segs, "segs", I32); _req(o, "o", F32)
+    M = q.shape[0]
+    if tuple(o.shape) != (M, H * vdim) or tuple(state_S.shape[1:]) != (H, vdim, dim) or q.shape[1] != H * dim or v.shape[1] != H * vdim:
+        raise _lib.LiaError("forget_scan: shapes do not agree")
+    check(_lib.load().lia_forget_scan(_p(q), _p(f), ld, _p(v), ldv, _p(state_S), _p(segs), segs.shape[0], H, dim, vdim, _p(o), _stream()),
+          "lia_forget_scan")
+    count_launches()
+    return o
+
+
+def diff_combine(a, out, H, G, vdim, lam, mult, eps):
+    """a [M, G, 2, H // G, vdim] fp32 (two attention maps per query head, grouped by key/value head) -> out [M, H * vdim]:
+    o = a1 - lam * a2, out = mult * o / rms(o) per head."""
+    _req(a, "a", F32)
+    M = a.shape[0]
+    if a.numel() != M * 2 * H * vdim or not (out.is_cuda and out.is_contiguous() and tuple(out.shape) == (M, H * vdim)):
+        raise _lib.LiaError("diff_combine: a must hold [M, 2 H vdim] numbers, out a contiguous [M, H * vdim] tensor")
+    check(_lib.load().lia_diff_combine(_p(a), _p(out), _f32(out), M, H, G, vdim, float(lam), float(mult), float(eps), _stream()), "lia_diff_combine")
     count_launches()
     return out
