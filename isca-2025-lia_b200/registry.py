@@ -32,6 +32,11 @@ def _bizetar():
     return BizetarForCausalLM
 
 
+def _zatusun():
+    from .modeling_zatusun import ZatusunForCausalLM
+    return ZatusunForCausalLM
+
+
 register("OPTForCausalLM", _opt)
 register("opt", _opt)
 register("Davasun", _davasun)
@@ -40,6 +45,8 @@ register("Bebulorn", _bebulorn)
 register("BebulornForCausalLM", _bebulorn)
 register("Bizetar", _bizetar)
 register("BizetarForCausalLM", _bizetar)
+register("Zatusun", _zatusun)
+register("ZatusunForCausalLM", _zatusun)
 
 
 def architecture_of(path):

@@ -1,7 +1,8 @@
 """Sequence mixers and feed-forwards that run on a 32-bit residual stream, each with its constants as parameters so that
 any model design can assemble them: a matrix-memory recurrent mixer (mLSTM), attention over a latent key/value cache with
-a partly rotated query/key and an output gate, linear attention with a fixed decay per head, the gated delta rule behind a
-short convolution, sliding-window attention with grouped key/value heads, attention over the whole history with a sink in the
+a partly rotated query/key and an output gate (queries direct or through a latent of their own), linear attention with a fixed
+decay per head, linear attention with a forget gate per channel, the gated delta rule behind a short convolution, differential
+attention (two softmax maps over shared values, subtracted) under a chunked or sliding mask, sliding-window attention with grouped key/value heads, attention over the whole history with a sink in the
 softmax (behind an optional bias, convolution, norm, temperature and rotation of its inputs, with a distance bias, a blend of
 values across layers and an output gate), and the feed-forwards -- clamped gated, plain gated with any activation, one with a
 polynomial activation between norms, and a routed mixture of experts (plain or gated experts, a shared expert, experts that
@@ -120,21 +121,43 @@ def rotary_inv_freq(dims, base, device):
 class LatentAttentionMixer:
     """Attention over a latent cache: per token one normalised latent (kv_rank) and one rotated key part (rot_dim) shared by
     the heads are cached; head h's unrotated key and value are Wuk_h c and Wuv_h c.  Queries are laid out per head as
-    [dim unrotated | rot_dim rotated]; rotary "rotate half" over the first ``rot_dims`` channels of the rotated part;
-    causal softmax with ``scale``; head outputs times sigmoid(Wg h)_h; then Wo.  The kernels work in the latent space
-    (csrc/latent_attn.cu), so Wuk is applied to the query and Wuv to the attention's output."""
+    [dim unrotated | rot_dim rotated]; causal softmax with ``scale``; then Wo.  The kernels work in the latent space
+    (csrc/latent_attn.cu), so Wuk is applied to the query and Wuv to the attention's output.  Options:
+      ``q_rank``      None: q = Wq h ("q"); a number: q = Wuq RMSnorm(Wdq h) with the plain weight "dq.norm" ("dq", "uq");
+      ``rot_pairs``   False: rotary "rotate half" over the first ``rot_dims`` channels of the rotated part (fp32 angles);
+                      True: channels (2i, 2i+1) turn together, angles from float64 frequencies, ``rot_scaling`` interpolates them
+                      (``scaled_rotary_freq``) and sets the amplitude of cos and sin;
+      ``gate``        "head": head outputs times sigmoid(Wg h)_h ("g" [H, W]); "channel": the concatenated heads times
+                      sigmoid(Wg h) element by element ("g" [H * vdim, W]); None: no gate."""
 
-    def __init__(self, w, heads, dim, rot_dim, vdim, kv_rank, rot_dims, rot_base, scale, norm_eps, dtype, device):
+    def __init__(self, w, heads, dim, rot_dim, vdim, kv_rank, rot_dims, rot_base, scale, norm_eps, dtype, device, q_rank=None, rot_pairs=False,
+                 rot_scaling=None, gate="head"):
+        if gate not in (None, "head", "channel"):
+            raise ValueError(f"unknown output gate {gate!r}")
+        if rot_dims % 2 or not 0 <= rot_dims <= rot_dim:
+            raise ValueError(f"cannot rotate {rot_dims} of {rot_dim} channels")
+        if rot_scaling and not rot_pairs:
+            raise ValueError("interpolated frequencies come with the pairwise rotation")
         self.H, self.dim, self.rot, self.vdim, self.rank = heads, dim, rot_dim, vdim, kv_rank
         self.rot_dims, self.scale, self.eps, self.dtype = rot_dims, float(scale), float(norm_eps), dtype
-        self.proj = Linear([w["q"], w["dkv"]], dtype, device)
-        self.w_gate = w["g"].to(device=device, dtype=dtype).contiguous()
+        self.q_rank, self.gate, self.rot_pairs = q_rank, gate, bool(rot_pairs)
+        stacked = [w["dq"] if q_rank else w["q"], w["dkv"]] + ([w["g"]] if gate == "channel" else [])
+        self.proj = Linear(stacked, dtype, device)
+        if q_rank:
+            self.q_norm_w = w["dq.norm"].to(device=device, dtype=F32).contiguous()
+            self.up_q = Linear([w["uq"]], dtype, device)
+        self.w_gate = w["g"].to(device=device, dtype=dtype).contiguous() if gate == "head" else None
         self.c_norm_w = w["dkv.norm"].to(device=device, dtype=F32).contiguous()
         # Wuk [H*dim, rank] -> per head [rank, dim]: the projection that carries a query into the latent space
         self.w_uk_t = w["uk"].to(device=device, dtype=dtype).view(heads, dim, kv_rank).transpose(1, 2).contiguous()
         self.w_uv = w["uv"].to(device=device, dtype=dtype).contiguous()            # [H*vdim, rank]
         self.out = Linear([w["o"]], dtype, device)
-        self.inv_freq = rotary_inv_freq(rot_dims, rot_base, device)
+        self.rot_mag = 1.0
+        if self.rot_pairs:
+            f, self.rot_mag = scaled_rotary_freq(rot_dims, rot_base, rot_scaling)
+            self.inv_freq = f.to(device).contiguous()                                    # float64
+        else:
+            self.inv_freq = rotary_inv_freq(rot_dims, rot_base, device)
 
     def new_state(self, slots):
         return (slots.add_rows(self.rank + self.rot, self.dtype),)
@@ -144,19 +167,29 @@ class LatentAttentionMixer:
         M, H, D = h.shape[0], self.H, self.rank + self.rot
         y = self.proj(h)
         q, dkv = self.proj.part(y, 0), self.proj.part(y, 1)
-        gate = torch.empty(M, H, dtype=F32, device=h.device)
-        ops.linear_small(h, self.w_gate, None, gate, ops.GATE_SIGMOID)
+        if self.q_rank:
+            cq = torch.empty(M, self.q_rank, dtype=self.dtype, device=h.device)
+            ops.rms_norm_rows(q, self.q_norm_w, cq, self.eps)
+            q = self.up_q(cq)
+        gate = None
+        if self.gate == "head":
+            gate = torch.empty(M, H, dtype=F32, device=h.device)
+            ops.linear_small(h, self.w_gate, None, gate, ops.GATE_SIGMOID)
         qa = torch.empty(M, H * D, dtype=F32, device=h.device)
         ops.latent_prep(q, dkv, self.c_norm_w, self.inv_freq, batch.meta, cache, qa, H, self.dim, self.rot, self.rot_dims, self.rank,
-                        self.eps)
+                        self.eps, pairs=self.rot_pairs, rot_mag=self.rot_mag)
         # q~[m, h, :rank] = Wuk_h^T q[m, h, :dim]
         ops.linear_plain(q, self.w_uk_t, qa, batch=H, a_batch_stride=self.dim + self.rot, w_batch_stride=self.rank * self.dim,
                          out_batch_stride=D, n=self.rank, k=self.dim)
         lat = torch.empty(M, H * self.rank, dtype=F32, device=h.device)
         ops.latent_attn(qa, cache, batch.meta, gate, lat, H, self.rank, self.rot, self.scale, batch.max_ctx)
-        o = torch.empty(M, H * self.vdim, dtype=self.dtype, device=h.device)
+        channel = self.gate == "channel"
+        o = torch.empty(M, H * self.vdim, dtype=F32 if channel else self.dtype, device=h.device)
         ops.linear_plain(lat, self.w_uv, o, batch=H, a_batch_stride=self.rank, w_batch_stride=self.vdim * self.rank,
                          out_batch_stride=self.vdim, n=self.vdim, k=self.rank)
+        if channel:
+            og = torch.empty(M, H * self.vdim, dtype=self.dtype, device=h.device)
+            o = ops.sigmoid_mul(o, self.proj.part(y, 2), og)
         return self.out(o)
 
 
@@ -278,6 +311,107 @@ class WindowAttentionMixer:
         o = torch.empty(M, self.H * self.vdim, dtype=self.dtype, device=h.device)
         ops.window_attn(q, kc, vc, batch.meta, self.temp, o, self.H, self.G, self.dim, self.vdim, self.window, self.scale, self.softcap,
                         nseg=batch.segs.shape[0], max_ctx=batch.max_ctx)
+        return self.out(o)
+
+
+class ForgetGateLinearAttentionMixer:
+    """Keyless linear attention whose per-channel forget gate f doubles as the write strength 1 - f (HGRN2's recurrence): q = silu(Wq h), v = Wv h,
+    f = low + (1 - low) * sigmoid(Wf h + bf) per head and channel with the learned lower bound ``low``; per head
+    row d of the state follows S[d] <- f[d] S[d] + (1 - f[d]) v and the output is o = sum_d q[d] S[d] (no key, no further scale; csrc/linear_scan.cu); each head's o RMS-normed
+    over vdim with a plain weight shared by the heads; then Wo.  Gates, state and sums are fp32."""
+
+    def __init__(self, w, heads, dim, vdim, norm_eps, dtype, device):
+        self.H, self.dim, self.vdim, self.eps, self.dtype = heads, dim, vdim, float(norm_eps), dtype
+        self.proj = Linear([w["q"], w["f"], w["v"]], dtype, device)
+        self.f_bias = w["f.b"].to(device=device, dtype=F32).contiguous()
+        self.low = w["lower"].to(device=device, dtype=F32).contiguous()
+        self.norm_w = w["norm"].to(device=device, dtype=F32).repeat(heads).contiguous()
+        self.out = Linear([w["o"]], dtype, device)
+
+    def new_state(self, slots):
+        return (slots.add_recurrent((self.H, self.vdim, self.dim)),)
+
+    def __call__(self, h, batch, state):
+        (S,) = state
+        M, nq, nv = h.shape[0], self.H * self.dim, self.H * self.vdim
+        y = self.proj(h)
+        qfv = torch.empty(M, 2 * nq + nv, dtype=F32, device=h.device)
+        ops.forget_gate_prep(y, self.proj.offsets, self.f_bias, self.low, qfv, nq, nv)
+        o = torch.empty(M, nv, dtype=F32, device=h.device)
+        ops.forget_scan(qfv[:, :nq], qfv[:, nq:2 * nq], qfv[:, 2 * nq:], S, batch.segs, self.H, self.dim, self.vdim, o)
+        on = torch.empty(M, nv, dtype=self.dtype, device=h.device)
+        ops.headnorm_gate(o, self.norm_w, None, on, self.H, self.vdim, self.eps)
+        return self.out(on)
+
+
+def wavelength_scaled_rotary_freq(dims, base, scaling=None):
+    """Rotation frequencies f_i = base^(-2i/dims), i < dims/2, as float64.  With ``scaling`` {factor, low, high, original}
+    (the rule Llama 3.1 uses): a pair whose wavelength 2 pi / f is shorter than original / high keeps f, one longer than
+    original / low gets f / factor, and between the two the blend weight t = (original / wavelength - low) / (high - low)
+    gives f * (t + (1 - t) / factor)."""
+    import math
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = float(base) ** (-2.0 * i / dims)
+    if not scaling:
+        return f
+    factor, low, high, original = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+    wave = 2.0 * math.pi / f
+    t = (original / wave - low) / (high - low)
+    mid = f * (t + (1.0 - t) / factor)
+    return torch.where(wave < original / high, f, torch.where(wave > original / low, f / factor, mid))
+
+
+class DifferentialAttentionMixer:
+    """Differential attention with grouped key/value heads: every query head carries two softmax attention maps (q and k have
+    2 * dim channels per head, [map 1 | map 2]) over the SAME values; with a1, a2 the maps' outputs,
+    o = a1 - lam * a2, then o / rms(o) per head (no weight) times (1 - diff), then Wo;
+    lam = exp(lq1 . lk1) - exp(lq2 . lk2) + diff is a single scalar per layer.  q and k turn in channel pairs (2i, 2i+1) over the
+    first ``rot["dims"]`` channels of every map (``rot["scaling"]``: the wavelength rule).  Mask: causal, and ``chunk`` > 0 keeps
+    only the keys of the query's own block of ``chunk`` positions, ``window`` > 0 only the last ``window`` positions.
+    The key cache holds 2 G heads ([g][map]), the value cache G; the query projection's rows are regrouped at load time as
+    [g][map][head of the group] so that the attention kernel's plain grouping (csrc/window_attn.cu) pairs every map with its key
+    head, and value head = key head // 2.  Scores, weights, sums, the difference and the norm are fp32."""
+
+    def __init__(self, w, heads, kv_heads, dim, vdim, scale, diff, norm_eps, dtype, device, rot=None, chunk=0, window=0):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} heads do not divide into {kv_heads} key/value heads")
+        self.H, self.G, self.dim, self.vdim = heads, kv_heads, dim, vdim
+        self.scale, self.diff, self.eps, self.dtype = float(scale), float(diff), float(norm_eps), dtype
+        self.chunk, self.window = int(chunk or 0), int(window or 0)
+        rep = heads // kv_heads
+        wq = w["q"].view(kv_heads, rep, 2, dim, -1).permute(0, 2, 1, 3, 4).reshape(heads * 2 * dim, -1)      # [g][r][map] -> [g][map][r]
+        self.proj = Linear([wq, w["k"], w["v"]], dtype, device)
+        d64 = torch.float64
+        self.lam = float(torch.exp((w["lq1"].to(d64) * w["lk1"].to(d64)).sum()) - torch.exp((w["lq2"].to(d64) * w["lk2"].to(d64)).sum())) + self.diff
+        self.rot_dims, self.freq = 0, None
+        if rot:
+            self.rot_dims = int(rot["dims"])
+            if self.rot_dims % 2 or not 0 < self.rot_dims <= dim:
+                raise ValueError(f"cannot rotate {self.rot_dims} of {dim} channels")
+            self.freq = wavelength_scaled_rotary_freq(self.rot_dims, rot["base"], rot.get("scaling")).to(device).contiguous()
+        self.out = Linear([w["o"]], dtype, device)
+
+    @property
+    def span(self):
+        """The most keys a query can see (0: the whole history)."""
+        lim = [n for n in (self.chunk, self.window) if n > 0]
+        return min(lim) if lim else 0
+
+    def new_state(self, slots):
+        return (slots.add_rows(2 * self.G * self.dim, self.dtype), slots.add_rows(self.G * self.vdim, self.dtype))
+
+    def __call__(self, h, batch, state):
+        kc, vc = state
+        M, H2, G2 = h.shape[0], 2 * self.H, 2 * self.G
+        y = self.proj(h)
+        q = torch.empty(M, H2 * self.dim, dtype=F32, device=h.device)
+        ops.qkv_prep(y, self.proj.offsets, batch.meta, q, kc, vc, H2, G2, self.dim, self.vdim, self.eps, freq=self.freq, rot_dims=self.rot_dims,
+                     v_heads=self.G)
+        a = torch.empty(M, H2 * self.vdim, dtype=F32, device=h.device)
+        ops.window_attn(q, kc, vc, batch.meta, None, a, H2, G2, self.dim, self.vdim, self.window, self.scale, 0.0, nseg=batch.segs.shape[0],
+                        max_ctx=batch.max_ctx, chunk=self.chunk, v_div=2)
+        o = torch.empty(M, self.H * self.vdim, dtype=self.dtype, device=h.device)
+        ops.diff_combine(a, o, self.H, self.G, self.vdim, self.lam, 1.0 - self.diff, self.eps)
         return self.out(o)
 
 
@@ -451,7 +585,9 @@ class MoEFeedForward:
     """Routed mixture of experts: router logits in fp32, softmax over all experts, the ``top`` largest scores (``correction``,
     one number per router output, is added for the choice only) as weights, renormalised (divided by their sum + 1e-20) if
     ``renorm``; every expert is Wdown act(Wup h), or Wdown (act(Wgate h) * Wup h) when ``experts_w`` carry a "gate"; the last
-    ``identity`` router outputs are experts without weights that hand the token back; a shared expert (optional) runs for
+    ``identity`` router outputs are experts without weights that hand the token back; ``act`` = ops.ACT_CLAMPED_SWISH with
+    ``act_params`` = (limit, alpha) makes a gated expert Wdown (g' sigmoid(alpha g') (u' + 1)), g' = min(Wgate h, limit), u' = clamp(Wup h, +-limit);
+    with ``renorm`` the weights equal a softmax restricted to the selected experts' logits; a shared expert (optional) runs for
     every token and is added.  ``experts_w``: list of {"up", "down"[, "gate"]} per expert.  The (token, choice) pairs are
     grouped by expert on the device (no host round trip) and each projection runs as one grouped launch; a handful of pairs
     (decoding) take the form with one warp per output instead.  The result is fp32."""
@@ -459,8 +595,9 @@ class MoEFeedForward:
     FEW_PAIRS = 48            # up to here: one warp per output, no plan
     TENSOR_CORE_PAIRS = 512   # from here (bf16, sizes that are multiples of 8): every expert's rows through the tensor-core GEMM
 
-    def __init__(self, router_w, experts_w, top, ff, act, shared, dtype, device, correction=None, renorm=True, identity=0):
+    def __init__(self, router_w, experts_w, top, ff, act, shared, dtype, device, correction=None, renorm=True, identity=0, act_params=(0.0, 0.0)):
         self.E, self.top, self.ff, self.act, self.dtype = len(experts_w), int(top), ff, act, dtype
+        self.act_params = (float(act_params[0]), float(act_params[1]))      # ACT_CLAMPED_SWISH (gated experts): (limit, alpha)
         self.identity, self.renorm = int(identity), bool(renorm)
         self.R = self.E + self.identity                          # router outputs
         if not 1 <= self.top <= self.R or self.E < 1 or router_w.shape[0] != self.R:
@@ -506,7 +643,10 @@ class MoEFeedForward:
         ys = torch.empty(used, W, dtype=self.dtype, device=dev)
         if rows:
             ops.moe_expert_gemms(xs, self.w_up, up, counts, tm, self._workspace(rows, n_up, W, dev))
-            ops.gated_act(up, ff, mid, self.act, up_off=ff if self.gated else -1)
+            if self.act == ops.ACT_CLAMPED_SWISH:
+                ops.clamped_glu(up, ff, ff, mid, *self.act_params)
+            else:
+                ops.gated_act(up, ff, mid, self.act, up_off=ff if self.gated else -1)
             ops.moe_expert_gemms(mid, self.w_down, ys, counts, tm, self._workspace(rows, W, ff, dev))
         ops.moe_combine(ys, self.shared(h) if self.shared is not None else None, y, top, pos_of=pos_of, wt=wt,
                         identity=(idx, E, h, wt) if self.identity else None)
@@ -530,7 +670,7 @@ class MoEFeedForward:
         ypair = torch.empty(pairs, W, dtype=F32, device=dev)
         if pairs <= self.FEW_PAIRS:
             mid = torch.empty(pairs, self.ff, dtype=self.dtype, device=dev)
-            ops.moe_gemm(h, self.w_up, mid, idx, wt, top, True, self.act, gated=self.gated)
+            ops.moe_gemm(h, self.w_up, mid, idx, wt, top, True, self.act, gated=self.gated, act_params=self.act_params)
             ops.moe_gemm(mid, self.w_down, ypair, idx, wt, top, False)
         else:
             n_tiles, tm = ops.moe_tiles(pairs, R)
@@ -539,7 +679,7 @@ class MoEFeedForward:
             pos_of = torch.empty(pairs, dtype=torch.int32, device=dev)
             ops.moe_plan(idx, R, perm, tile_expert, pos_of)
             mid = torch.empty(n_tiles * tm, self.ff, dtype=self.dtype, device=dev)
-            ops.moe_gemm(h, self.w_up, mid, idx, wt, top, True, self.act, perm, tile_expert, gated=self.gated)
+            ops.moe_gemm(h, self.w_up, mid, idx, wt, top, True, self.act, perm, tile_expert, gated=self.gated, act_params=self.act_params)
             ops.moe_gemm(mid, self.w_down, ypair, idx, wt, top, False, ops.ACT_NONE, perm, tile_expert)
         ops.moe_combine(ypair, self.shared(h) if self.shared is not None else None, y, top, identity=identity)
         return y
