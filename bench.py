@@ -66,6 +66,8 @@ def parse():
                     help="instead of the headline workload: the same comparison for Bebulorn beside Davasun, its closest existing model")
     ap.add_argument("--compare-bizetar", action="store_true",
                     help="instead of the headline workload: the same comparison for Bizetar beside Bebulorn, its closest existing model")
+    ap.add_argument("--compare-zatusun", action="store_true",
+                    help="instead of the headline workload: the same comparison for Zatusun beside Bebulorn, its closest existing model")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
@@ -412,6 +414,11 @@ def _main(args, json_out):
         from lia_b200 import bench_compare
         if rank == 0:
             json_out.write(json.dumps(bench_compare.run_bizetar(peaks())) + "\n")
+        return 0
+    if args.compare_zatusun:
+        from lia_b200 import bench_compare
+        if rank == 0:
+            json_out.write(json.dumps(bench_compare.run_zatusun(peaks())) + "\n")
         return 0
     from lia_b200.modeling_opt import get_config
     cfg = get_config(args.model)

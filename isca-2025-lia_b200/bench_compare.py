@@ -4,6 +4,8 @@ beside OPT -- the closest existing model -- at equal width and depth, with every
 attention mixers on a 32-bit residual stream).
 `bench.py --compare-bizetar`: the same for Bizetar beside Bebulorn, the closest existing model (softmax attention with grouped
 key/value heads on the same attention kernel, dense and mixture-of-experts feed-forwards, step-served).
+`bench.py --compare-zatusun`: the same for Zatusun beside Bebulorn, the closest existing model (a matrix-state recurrence, masked
+softmax attention and routed experts on the same kernels, a looped block, step-served).
 
 Each operation of ``ops`` is wrapped for the duration of an instrumented pass: CUDA events around the call, and the
 operation's algorithmic FLOPs and bytes from its arguments.  roofline time = max(FLOPs / peak, bytes / HBM bandwidth)
@@ -55,6 +57,10 @@ def _cost(name, a, kw):
         state = 2.0 * segs.shape[0] * H * dim * vdim * 4
         per_token = 8.0 if kw.get("gates") is not None else 4.0                    # delta: two dot products and two updates per cell
         return per_token * M * H * dim * vdim, state + M * (2 * G * dim + H * vdim) * q.element_size() + _nbytes(o), "f32"
+    if name == "forget_scan":
+        q, S, segs, H, dim, vdim, o = a[0], a[3], a[4], a[5], a[6], a[7], a[8]
+        M = q.shape[0]
+        return 4.0 * M * H * dim * vdim, 2.0 * segs.shape[0] * H * dim * vdim * 4 + M * H * (2 * dim + vdim) * 4 + _nbytes(o), "f32"
     if name == "window_attn":
         q, kc, out, H, G, dim, vdim = a[0], a[1], a[5], a[6], a[7], a[8], a[9]
         keys = float(kw.get("_wkeys", 0))                                          # sum over rows of keys inside the window
@@ -98,7 +104,8 @@ class Instrument:
     NAMES = ("gemm", "linear_plain", "linear_small", "mlstm_scan", "headnorm_gate", "latent_prep", "latent_attn", "clamped_glu",
              "rms_add_norm", "embed_rmsnorm", "rms_gather", "layernorm", "attn_prefill", "attn_decode", "embed", "argmax", "argmax_f32",
              "linear_scan", "conv_prep", "conv_state_update", "kv_store", "window_attn", "ln_add_norm", "embed_rows", "ln_gather", "gated_act",
-             "router_topk", "moe_plan", "moe_gemm", "moe_gather", "moe_expert_gemms", "moe_combine", "qkv_prep", "gated_rms_add", "poly_norm")
+             "router_topk", "moe_plan", "moe_gemm", "moe_gather", "moe_expert_gemms", "moe_combine", "qkv_prep", "gated_rms_add", "poly_norm",
+             "embed_scale_pos", "residual_norm", "rms_norm_rows", "sigmoid_mul", "softcap", "forget_gate_prep", "forget_scan", "diff_combine")
 
     def __init__(self):
         self.records, self.saved, self.extra = [], {}, {}
@@ -189,12 +196,37 @@ def bizetar_config(width, n_layers):
     return {"architecture": "Bizetar", "vocab": 32000, "width": width, "layers": [pattern[i % 4] for i in range(n_layers)], "norm": {"eps": 1e-6}}
 
 
+def zatusun_config(width, n_runs):
+    """Layer sizes of a ~1-3 B model in ``n_runs`` layer runs: latent attention with heads of 128 + 64 query/key channels, a 512-wide
+    latent and queries through a latent of half the width; the forget-gate recurrence with heads of 128 x 128; differential
+    attention with two maps of 128 channels and values of 256 per head on 4 key/value heads, in chunks of 1024; every layer with
+    16 clamped gated experts of 0.6875 x (2 chosen).  Order: latent, recurrence (these two form the loop, run twice), then
+    latent, differential, recurrence, ... for the rest."""
+    H = width // 128
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": width * 11 // 16, "limit": 7.0}}
+    la = {"type": "latent_attention", "mlp": moe,
+          "mixer": {"heads": H, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": width // 2, "scale": 192 ** -0.5,
+                    "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}}
+    hg = {"type": "hgrn2", "mlp": moe, "mixer": {"heads": H, "dim": 128, "vdim": 128}}
+    Hd = max(1, width // 256)
+    di = {"type": "attention", "mlp": moe,
+          "mixer": {"heads": Hd, "kv_heads": min(4, Hd), "dim": 128, "vdim": 256, "diff": 0.5, "mask": {"size": 1024}, "scale": 128 ** -0.5,
+                    "rot": {"dims": 128, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 1024}}}}
+    rest = [la, di, hg]
+    layers = [la, hg] + [rest[i % 3] for i in range(max(n_runs - 4, 0))]
+    return {"architecture": "Zatusun", "vocab": 32000, "width": width, "max_positions": 8192, "layers": layers, "loop": {"start": 0, "stop": 2, "times": 2},
+            "norm": {"eps": 1e-6}, "embedding": {"scale": float(width) ** 0.5}, "logit_softcap": 30.0}
+
+
 def _window_keys(layers, n_new, ctx_before):
     """Sum over the new rows of the keys inside the first attention layer's window (the whole history where a layer names
     none), and the cached rows those windows span."""
-    win = next((l["mixer"].get("mask", {}).get("size", 1 << 30) for l in layers if l["type"].startswith("attention")), 0)
+    first = next((l for l in layers if l["type"].startswith("attention")), None)
+    win = first["mixer"].get("mask", {}).get("size", 1 << 30) if first else 0
     if not win:
         return 0, 0
+    if "diff" in first["mixer"]:              # a chunked mask: a row sees the keys of its own block of `win` positions
+        return sum((ctx_before + i) % win + 1 for i in range(n_new)), min(ctx_before + n_new, win + n_new - 1)
     keys = sum(min(win, ctx_before + i + 1) for i in range(n_new))
     return keys, min(ctx_before + n_new, win + n_new - 1)
 
@@ -249,6 +281,27 @@ def run_bebulorn(pk, widths=(2048, 4096), n_layers=8, prompt=2048, decode_ctx=20
         rec = {"width": width, "layers": n_layers, "prompt": prompt, "decode_context": decode_ctx}
         for name, make in (("bebulorn", lambda: BebulornForCausalLM(BebulornConfig.from_dict(bebulorn_config(width, n_layers)), dev, BF16)),
                            ("davasun", lambda: DavasunForCausalLM(DavasunConfig.from_dict(davasun_config(width, n_layers)), dev, BF16))):
+            m = make().init_weights(seed=1)
+            rec[name] = step_model(m, m.config, pk, g, prompt, decode_ctx, decode_batches, new)
+            del m
+            torch.cuda.empty_cache()
+        out["sizes"].append(rec)
+    return out
+
+
+def run_zatusun(pk, widths=(2048, 4096), n_layers=8, prompt=2048, decode_ctx=2048, decode_batches=(1, 16), new=16):
+    """Zatusun beside Bebulorn at equal width and number of layer runs."""
+    from .modeling_bebulorn import BebulornConfig, BebulornForCausalLM
+    from .modeling_zatusun import ZatusunConfig, ZatusunForCausalLM
+    dev = torch.device("cuda", 0)
+    props = torch.cuda.get_device_properties(dev)
+    pk = dict(pk, fp32_nominal_tflops=props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12)
+    out = {"peaks": pk, "sizes": []}
+    g = torch.Generator().manual_seed(0)
+    for width in widths:
+        rec = {"width": width, "layers": n_layers, "prompt": prompt, "decode_context": decode_ctx}
+        for name, make in (("zatusun", lambda: ZatusunForCausalLM(ZatusunConfig.from_dict(zatusun_config(width, n_layers)), dev, BF16)),
+                           ("bebulorn", lambda: BebulornForCausalLM(BebulornConfig.from_dict(bebulorn_config(width, n_layers)), dev, BF16))):
             m = make().init_weights(seed=1)
             rec[name] = step_model(m, m.config, pk, g, prompt, decode_ctx, decode_batches, new)
             del m
